@@ -5,6 +5,8 @@ size and window) form a *group* with a page pool, block tables and tensors of it
 
     storage[layer_in_group][0=keys | 1=values][page][kv_head][token_in_page][head_dim]
 
+(a request for one plane has no values: its mixer keeps one vector per token and head)
+
 A page holds ``PAGE`` consecutive tokens of one sequence, for every layer of the group at
 once, so a sequence's block table (its list of pages) is shared by the group's layers.  One
 (page, head) is a contiguous ``PAGE x head_dim`` tile, the unit the attention kernels load.
@@ -41,7 +43,7 @@ def pages_for(n_tokens: int) -> int:
 class LayerKV:
     """One layer's view of its group: what the kernels need."""
     k: torch.Tensor            # [n_pages, n_kv_heads, PAGE, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor | None     # None in a store of one plane
     block_table: torch.Tensor  # int32 [n_slots, max_pages]
     page: int
     n_kv_heads: int
@@ -85,8 +87,10 @@ class CacheGroup:
         self.layers = list(layers)
         self.pool = PagePool(n_pages)
         self.max_pages = max(1, pages_for(max_seq_len))
+        if request.planes not in (1, 2):
+            raise ValueError(f"a cache request has 1 or 2 planes, not {request.planes}")
         self.storage = torch.zeros(
-            (len(self.layers), 2, n_pages, request.n_kv_heads, PAGE, request.head_dim),
+            (len(self.layers), request.planes, n_pages, request.n_kv_heads, PAGE, request.head_dim),
             dtype=dtype, device=device)
         self.block_table = torch.zeros((n_slots, self.max_pages), dtype=torch.int32, device=device)
         self._table_host = np.zeros((n_slots, self.max_pages), dtype=np.int32)
@@ -147,5 +151,5 @@ class CacheGroup:
     def layer_view(self, layer: int) -> LayerKV:
         i = self.layers.index(layer)
         r = self.request
-        return LayerKV(self.storage[i, 0], self.storage[i, 1], self.block_table, PAGE,
-                       r.n_kv_heads, r.head_dim, r.window)
+        return LayerKV(self.storage[i, 0], self.storage[i, 1] if r.planes > 1 else None,
+                       self.block_table, PAGE, r.n_kv_heads, r.head_dim, r.window)

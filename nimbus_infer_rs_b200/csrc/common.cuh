@@ -16,7 +16,7 @@
 // Element types of tensors handed to launchers.
 enum NbDType : int { NB_F32 = 0, NB_BF16 = 1 };
 // Activation applied in a matrix product's epilogue.
-enum NbAct : int { NB_ACT_NONE = 0, NB_ACT_GELU_TANH = 1, NB_ACT_GELU_ERF = 2 };
+enum NbAct : int { NB_ACT_NONE = 0, NB_ACT_GELU_TANH = 1, NB_ACT_GELU_ERF = 2, NB_ACT_SILU = 3 };
 
 // Error codes above the range of cudaError_t.
 #define NB_ERR_BAD_ARG 10001
@@ -173,14 +173,20 @@ __device__ __forceinline__ float nb_gelu_tanh_fast(float x) {
   const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
   return __fdividef(x, 1.0f + __expf(-2.0f * u));
 }
+// SiLU: x * sigmoid(x) = x / (1 + exp(-x))
+__device__ __forceinline__ float nb_silu(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float nb_silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float nb_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float nb_apply_act_fast(float x, int act) {
   if (act == NB_ACT_GELU_TANH) return nb_gelu_tanh_fast(x);
   if (act == NB_ACT_GELU_ERF) return nb_gelu_erf(x);
+  if (act == NB_ACT_SILU) return nb_silu_fast(x);
   return x;
 }
 __device__ __forceinline__ float nb_apply_act(float x, int act) {
   if (act == NB_ACT_GELU_TANH) return nb_gelu_tanh(x);
   if (act == NB_ACT_GELU_ERF) return nb_gelu_erf(x);
+  if (act == NB_ACT_SILU) return nb_silu(x);
   return x;
 }
 

@@ -14,8 +14,11 @@ import os
 
 import torch
 
-ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU = 0, 1, 2, 3
+# what a dense product's epilogue can apply
 ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GELU_ERF}
+# what the gate of a gated feed-forward (routed experts) can be
+GATE_ACTIVATIONS = {**ACTIVATIONS, "silu": ACT_SILU}
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 DECODE_TARGET_CTAS = 4 * 148   # CTAs the split 32-bit decode attention aims to put on the GPU
@@ -175,6 +178,22 @@ class CudaBackend:
         if x.shape[1] != d or gamma.numel() != d or (rows is None and x.shape[0] < n):
             raise KernelError("layernorm: shapes do not agree")
         self._call("nb_layernorm", _ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out),
+                   dtype_code(out.dtype), n, d, eps, self._stream())
+
+    def rmsnorm(self, x, gamma, eps, out, rows=None, x_col=0):
+        """out[r] = rms-norm of columns ``x_col .. x_col + d`` of row ``rows[r]`` (or ``r``) of the
+        fp32 matrix ``x``, times ``gamma`` (or 1 if ``None``); statistics in fp32."""
+        _check(x, "x", torch.float32, 2)
+        _check(out, "out", None, 2)
+        if gamma is not None:
+            _check(gamma, "gamma", torch.float32, 1)
+        if rows is not None:
+            _check(rows, "rows", torch.int32, 1)
+        n, d = out.shape
+        if x.shape[1] < x_col + d or (gamma is not None and gamma.numel() != d) or (
+                rows is None and x.shape[0] < n):
+            raise KernelError("rmsnorm: shapes do not agree")
+        self._call("nb_rmsnorm", _ptr(x), x.shape[1], x_col, _ptr(rows), _ptr(gamma), _ptr(out),
                    dtype_code(out.dtype), n, d, eps, self._stream())
 
     # -- matrix products --------------------------------------------------------------
@@ -443,6 +462,117 @@ class CudaBackend:
                    kv.page, n_heads, kv.n_kv_heads, kv.head_dim,
                    _ptr(out), dtype_code(out.dtype), out.shape[1], scale,
                    window, n_rows, self._stream())
+
+    # -- attention over a cached latent ------------------------------------------------
+    def latent_append(self, src, col, gamma, eps, layout, kv):
+        """The step's latents into the one-plane paged store ``kv``: columns ``col .. col +
+        kv.head_dim`` of the fp32 rows ``src``, rms-normed (times ``gamma``) on the way."""
+        _check(src, "src", torch.float32, 2)
+        if gamma is not None:
+            _check(gamma, "gamma", torch.float32, 1)
+        if kv.n_kv_heads != 1 or src.shape[1] < col + kv.head_dim:
+            raise KernelError("latent_append: the store must have one head of the latent's size")
+        self._call("nb_latent_append", _ptr(src), src.shape[1], col, _ptr(gamma), eps,
+                   _ptr(layout.row_slot), _ptr(layout.row_pos), _ptr(kv.k), dtype_code(kv.k.dtype),
+                   _ptr(kv.block_table), kv.block_table.shape[1], kv.page, kv.head_dim,
+                   layout.n_rows, self._stream())
+
+    def head_linear(self, x, x_col, w, out, layout, gate=None, gate_col=0):
+        """A linear map per head: ``out[r, h] = w[h] @ x[r, x_col + h*n_in : ...]`` with ``w``
+        ``[n_heads, n_out, n_in]``; with ``gate`` (fp32 rows, head ``h``'s logit at column
+        ``gate_col + h``) the head's result is multiplied by the logit's sigmoid."""
+        _check(x, "x", None, 2)
+        _check(w, "w", None, 3)
+        _check(out, "out", None, 2)
+        n_heads, n_out, n_in = w.shape
+        n = layout.n_rows
+        if x.shape[0] < n or out.shape[0] < n or x.shape[1] < x_col + n_heads * n_in \
+                or out.shape[1] != n_heads * n_out:
+            raise KernelError("head_linear: shapes do not agree")
+        if gate is not None:
+            _check(gate, "gate", torch.float32, 2)
+            if gate.shape[0] < n or gate.shape[1] < gate_col + n_heads:
+                raise KernelError("head_linear: gate shape does not match")
+        self._call("nb_head_linear", _ptr(x), dtype_code(x.dtype), x.shape[1], x_col, _ptr(w),
+                   dtype_code(w.dtype), _ptr(out), dtype_code(out.dtype), out.shape[1], _ptr(gate),
+                   gate.shape[1] if gate is not None else 0, gate_col, _ptr(layout.row_slot), n,
+                   n_heads, n_in, n_out, self._stream())
+
+    def attention_latent(self, q, layout, kv, n_heads, sink, out, scale, window=0):
+        """Causal attention of the packed rows over the cached latents of ``kv`` (one plane: a
+        token's latent is its key and its value, for every head).  ``q``: the heads' queries
+        mapped into the latent's space, ``[rows, n_heads * rank]``; ``sink``: fp32 ``[n_heads]``
+        logits of a key-less, value-less term of the softmax's denominator, or ``None``."""
+        _check(q, "q", None, 2)
+        _check(out, "out", None, 2)
+        rank = kv.head_dim
+        n = layout.n_rows
+        if kv.n_kv_heads != 1 or q.shape[1] != n_heads * rank or out.shape[1] != n_heads * rank \
+                or q.shape[0] < n or out.shape[0] < n:
+            raise KernelError("attention_latent: shapes do not agree")
+        if sink is not None:
+            _check(sink, "sink", torch.float32, 1)
+            if sink.numel() != n_heads:
+                raise KernelError("attention_latent: one sink per head")
+        self._call("nb_attention_latent", _ptr(q), dtype_code(q.dtype), q.shape[1], 0,
+                   _ptr(layout.row_slot), _ptr(layout.row_pos), _ptr(kv.k), dtype_code(kv.k.dtype),
+                   _ptr(kv.block_table), kv.block_table.shape[1], kv.page, n_heads, rank,
+                   _ptr(sink), _ptr(out), dtype_code(out.dtype), out.shape[1], scale, window, n,
+                   self._stream())
+
+    # -- routed experts ---------------------------------------------------------------
+    def moe_route(self, logits, col, n_experts, top, renormalize, layout, idx, weight):
+        """Per row: softmax over the ``n_experts`` fp32 logits at columns ``col ..``, the ``top``
+        largest (of equal scores the lower index) into ``idx`` / ``weight`` ``[rows, top]``."""
+        _check(logits, "logits", torch.float32, 2)
+        _check(idx, "idx", torch.int32, 2)
+        _check(weight, "weight", torch.float32, 2)
+        n = layout.n_rows
+        if logits.shape[0] < n or idx.shape != (n, top) or weight.shape != (n, top):
+            raise KernelError("moe_route: shapes do not agree")
+        self._call("nb_moe_route", _ptr(logits), logits.shape[1], col, _ptr(layout.row_slot), n,
+                   n_experts, top, 1 if renormalize else 0, _ptr(idx), _ptr(weight), self._stream())
+
+    def moe_group(self, idx, n_experts, offsets, order, place):
+        """Group the (row, choice) pairs of ``idx`` by expert: ``offsets`` ``[n_experts + 1]``,
+        ``order`` (place -> pair) and ``place`` (pair -> place, -1 for none), all int32."""
+        for t, nm in ((idx, "idx"), (offsets, "offsets"), (order, "order"), (place, "place")):
+            _check(t, nm, torch.int32)
+        n_pairs = idx.numel()
+        if offsets.numel() < n_experts + 1 or order.numel() < n_pairs or place.numel() < n_pairs:
+            raise KernelError("moe_group: shapes do not agree")
+        self._call("nb_moe_group", _ptr(idx), n_pairs, n_experts, _ptr(offsets), _ptr(order),
+                   _ptr(place), self._stream())
+
+    def moe_linear(self, x, order, row_div, offsets, w, w2, out, act=ACT_NONE):
+        """A product per expert over its group: ``out[place] = x[row(place)] @ w[e].T``, or
+        ``act(x @ w[e].T) * (x @ w2[e].T)`` with ``w2``; ``row(place) = order[place] // row_div``
+        with ``order``, else ``place``.  ``w``, ``w2``: ``[n_experts, N, K]``."""
+        _check(x, "x", None, 2)
+        _check(w, "w", None, 3)
+        _check(out, "out", None, 2)
+        n_experts, N, K = w.shape
+        if w2 is not None:
+            _check(w2, "w2", w.dtype, 3)
+            if w2.shape != w.shape:
+                raise KernelError("moe_linear: the two weight sets differ in shape")
+        if x.shape[1] != K or out.shape[1] != N or offsets.numel() < n_experts + 1:
+            raise KernelError("moe_linear: shapes do not agree")
+        self._call("nb_moe_gemm", _ptr(x), dtype_code(x.dtype), x.shape[1], _ptr(order), row_div,
+                   _ptr(offsets), n_experts, out.shape[0], _ptr(w), _ptr(w2), dtype_code(w.dtype),
+                   _ptr(out), dtype_code(out.dtype), out.shape[1], N, K, act, self._stream())
+
+    def moe_combine(self, y, place, weight, residual):
+        """``residual[r] += sum_k weight[r, k] * y[place[r, k]]`` (fp32, ``k`` in order)."""
+        _check(y, "y", torch.float32, 2)
+        _check(place, "place", torch.int32)
+        _check(weight, "weight", torch.float32, 2)
+        _check(residual, "residual", torch.float32, 2)
+        n, top = weight.shape
+        if residual.shape[0] < n or residual.shape[1] != y.shape[1] or place.numel() < n * top:
+            raise KernelError("moe_combine: shapes do not agree")
+        self._call("nb_moe_combine", _ptr(y), y.shape[1], _ptr(place), _ptr(weight), top,
+                   _ptr(residual), n, self._stream())
 
     def advance_decode(self, tokens, next_tokens, row_pos, row_slot):
         """tokens <- next_tokens, row_pos += 1 for live rows (between two decode steps)."""

@@ -286,6 +286,57 @@ NB_EXPORT int nb_layernorm(const float* x, const int* rows, const float* gamma, 
 }
 
 // ---------------------------------------------------------------------------------
+// Root-mean-square norm: out[r] = x[src] / sqrt(mean(x[src]^2) + eps) * gamma, statistics and
+// scaling in fp32.  The source rows are columns x_col .. x_col + d of a wider fp32 matrix of
+// row stride x_stride (so that a slice of a fused projection's result can be normed in
+// place of a copy); `rows` (optional) names the source row of every output row, a negative
+// entry gives zeros.  `gamma` may be null (no learned scale).
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* x, int x_stride, int x_col, const int* rows,
+                               const float* __restrict__ gamma, TOut* out, int d, float eps) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  TOut* o = out + (size_t)r * d;
+  if (src < 0) {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = nb_from_f32<TOut>(0.0f);
+    return;
+  }
+  const float* xr = x + (size_t)src * x_stride + x_col;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = xr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = nb_block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    o[i] = nb_from_f32<TOut>(xr[i] * inv * (gamma ? gamma[i] : 1.0f));
+}
+
+NB_EXPORT int nb_rmsnorm(const float* x, int x_stride, int x_col, const int* rows,
+                         const float* gamma, void* out, int out_dtype, int n_rows, int d, float eps,
+                         cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0 && x_col >= 0 && x_stride >= x_col + d, NB_ERR_BAD_ARG,
+             "rmsnorm: bad sizes rows=%d d=%d col=%d stride=%d", n_rows, d, x_col, x_stride);
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : (d >= 128 ? 128 : 64));
+  if (out_dtype == NB_F32)
+    NB_CUDA(nb_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, x_stride,
+                      x_col, rows, gamma, (float*)out, d, eps));
+  else if (out_dtype == NB_BF16)
+    NB_CUDA(nb_launch(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x,
+                      x_stride, x_col, rows, gamma, (__nv_bfloat16*)out, d, eps));
+  else
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "rmsnorm: unknown output dtype %d", out_dtype);
+  NB_CHECK_LAUNCH("rmsnorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
 // Append this step's keys and values to the paged cache (src/cache.rs:44-57 writes rows
 // P..P+T of every head).  Row r of `src` holds [.. | K: n_kv_heads*head_dim | V: same ..]
 // starting at column k_col / v_col; it goes to token `pos[r]` of sequence slot `slot[r]`.

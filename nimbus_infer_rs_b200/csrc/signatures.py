@@ -51,6 +51,15 @@ SIGNATURES = {
     "nb_get_overlap": "",
     "nb_embed_pos": "ppppipiip",
     "nb_layernorm": "pppppiiifp",
+    "nb_rmsnorm": "piipppiiifp",
+    "nb_latent_append": "piipfpppipiiiip",
+    "nb_head_linear": "piiipipiipiipiiiip",
+    "nb_attention_latent": "piiipppipiiiippiifiip",
+    "nb_moe_route": "piipiiiippp",
+    "nb_moe_group": "piipppp",
+    "nb_moe_gemm_tiles": "ii",
+    "nb_moe_gemm": "piipipiippipiiiiip",
+    "nb_moe_combine": "pippipip",
     "nb_kv_append": "piiiipppppiiiiip",
     "nb_advance_decode": "ppppip",
     "nb_repetition_penalty": "piipipfp",

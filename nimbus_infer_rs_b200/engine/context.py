@@ -19,3 +19,5 @@ class StepContext:
     kv: Any = None           # LayerKV or None
     state: Any = None        # fp32 [n_slots, n_elements] or None
     writes_cache: bool = True
+    # what a layer's mixer leaves for the feed-forward beside it: (fp32 rows, first column)
+    shared_projection: Any = None

@@ -7,6 +7,7 @@ from its own cached length, and returns logits at the rows asked for.
 """
 from __future__ import annotations
 
+from dataclasses import replace
 from pathlib import Path
 from typing import Callable, Sequence
 
@@ -14,7 +15,7 @@ import numpy as np
 import torch
 
 from .. import models  # noqa: F401  (registers the architectures)
-from ..cache import SequenceCache
+from ..cache import PAGE, SequenceCache, pages_for
 from ..config.registry import get_architecture, load_config
 from ..csrc import ops as ops_mod
 from ..sampling import BatchSampler, SamplingParams, SequenceSampler
@@ -26,11 +27,17 @@ from .generate import plan_batches, run_batch, token_budget
 from .model import PRECISIONS, Model, Runtime
 from .step_graphs import StepGraphs, q_bound, row_padding
 
+DEFAULT_CACHE_TOKENS = 16384   # the cache of a model that does not bound its sequences itself
+
 
 class Engine:
     def __init__(self, model: Model, config, *, cache_tokens: int | None = None,
                  n_slots: int | None = None):
         self.model = model
+        if model.spec.max_seq_len is None:
+            # nothing in the model bounds a sequence: the cache does (whole pages)
+            cache_tokens = cache_tokens or DEFAULT_CACHE_TOKENS
+            model.spec = replace(model.spec, max_seq_len=pages_for(cache_tokens) * PAGE)
         self.spec = model.spec
         self.config = config
         self.rt = model.rt
@@ -225,7 +232,7 @@ class Engine:
             return None if not seen else (seen[0] if len(seen) == 1 else seen)
 
         mixers = [l.mixer for l in spec.layers]
-        ffns = [l.ffn for l in spec.layers]
+        ffns = [l.ffn for l in spec.layers if l.ffn is not None]
         kv_req, _ = self.model.storage_requests()
         reqs = []
         for r in kv_req.values():
@@ -248,7 +255,8 @@ class Engine:
             "d_model": spec.width, "head_dim": one([r.head_dim for r in reqs]),
             "max_seq_len": spec.max_seq_len, "norm": kinds([spec.final_norm]
                                                            + [l.norm_mixer for l in spec.layers]
-                                                           + [l.norm_ffn for l in spec.layers]),
+                                                           + [l.norm_ffn for l in spec.layers
+                                                              if l.norm_ffn is not None]),
             "mixer": kinds(mixers), "ffn": kinds(ffns), "activation": arg(ffns, "activation"),
             "pos": spec.position.kind, "tie_head": spec.tie_head,
             "dtype": self.rt.precision, "cache_tokens": self.cache.cache_tokens,

@@ -38,12 +38,14 @@ class Layer:
         self.block = build_part("block", spec.block)
         self.norm_mixer = build_part("norm", spec.norm_mixer)
         self.mixer = build_part("mixer", spec.mixer)
-        self.norm_ffn = build_part("norm", spec.norm_ffn)
-        self.ffn = build_part("ffn", spec.ffn)
+        self.norm_ffn = build_part("norm", spec.norm_ffn) if spec.norm_ffn is not None else None
+        self.ffn = build_part("ffn", spec.ffn) if spec.ffn is not None else None
 
     def parts(self):
-        return {"norm_mixer": self.norm_mixer, "mixer": self.mixer,
-                "norm_ffn": self.norm_ffn, "ffn": self.ffn}
+        """The layer's parts that exist, by the name their parameters are listed under."""
+        named = {"norm_mixer": self.norm_mixer, "mixer": self.mixer,
+                 "norm_ffn": self.norm_ffn, "ffn": self.ffn}
+        return {k: v for k, v in named.items() if v is not None}
 
 
 class Model:
@@ -86,7 +88,7 @@ class Model:
         """True if every part of the model may run under CUDA-graph capture."""
         parts = [self.embedding, self.position, self.final_norm, self.head]
         for l in self.layers:
-            parts += [l.block, l.norm_mixer, l.mixer, l.norm_ffn, l.ffn]
+            parts += [l.block, *l.parts().values()]
         return all(getattr(p, "graph_safe", False) for p in parts)
 
     def n_params(self) -> int:

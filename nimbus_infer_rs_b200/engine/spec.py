@@ -3,8 +3,11 @@
 An architecture's ``build_spec(config)`` returns a :class:`ModelSpec`; the engine builds the
 model from it without knowing the architecture.  Layers may differ from one another
 (another mixer, another feed-forward), ``schedule`` lists the layers in the order they run
-(a layer may be named twice), and a layer with ``cache_from`` set reads the key/value cache
-of that other layer instead of keeping its own.
+(a layer may be named twice: it then runs with the same parameters and a cache or state of
+its own each time), and a layer with ``cache_from`` set reads the key/value cache of that
+other layer instead of keeping its own.  A layer may have no feed-forward (``ffn=None``), and
+an arrangement in which both sublayers read one norm has no second norm (``norm_ffn=None``).
+``max_seq_len=None``: nothing in the model bounds a sequence; the cache's size does.
 """
 from __future__ import annotations
 
@@ -16,9 +19,9 @@ from ..parts.base import PartSpec
 @dataclass(frozen=True)
 class LayerSpec:
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: PartSpec | None
     norm_mixer: PartSpec
-    norm_ffn: PartSpec
+    norm_ffn: PartSpec | None
     block: PartSpec = PartSpec("pre_norm")
     cache_from: int | None = None
 
@@ -28,7 +31,7 @@ class ModelSpec:
     architecture: str
     vocab_size: int
     width: int
-    max_seq_len: int
+    max_seq_len: int | None
     position: PartSpec
     layers: tuple[LayerSpec, ...]
     final_norm: PartSpec

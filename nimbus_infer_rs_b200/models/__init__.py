@@ -1,2 +1,3 @@
 """Architectures known to the registry.  Importing this package registers them."""
 from . import gpt2  # noqa: F401
+from . import runesun  # noqa: F401

@@ -2,9 +2,11 @@ from .base import (INDEX, MATRIX, TABLE, VECTOR, Block, DeferredNorm, FeedForwar
                    ParamSpec, Part, PartSpec, Position, StateRequest, bind_params, build_part,
                    collect_param_specs, register_part, registered_parts)
 from .linear import Linear
-from .norm import LayerNorm
+from .norm import LayerNorm, RMSNorm
 from .position import LearnedAbsolute, NoPosition
 from .embedding import LMHead, TokenEmbedding
 from .attention import CausalSelfAttention
+from .latent_attention import LatentAttention
 from .feed_forward import DenseMLP
-from .block import PreNormBlock
+from .routed_experts import RoutedExperts
+from .block import ParallelBlock, PreNormBlock

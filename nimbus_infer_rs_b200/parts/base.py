@@ -17,7 +17,8 @@ family         interface
                (``ctx.kv``, ``ctx.state``, ``ctx.writes_cache``).
 ``ffn``        ``forward(ctx, h, residual)``: per-token feed-forward, ``residual += ffn(h)``
 ``block``      ``forward(ctx, x, layer)``: the arrangement of norms, mixer and feed-forward
-               around the residual stream of one layer
+               around the residual stream of one layer (``layer.ffn`` and ``layer.norm_ffn``
+               are ``None`` in a layer without them)
 =============  ===========================================================================
 
 Every part lists its parameters with :meth:`Part.param_specs` (shape and role) and gets the
@@ -56,10 +57,13 @@ class PartSpec:
 @dataclass(frozen=True)
 class KVRequest:
     """Growing per-sequence storage a mixer needs: keys and values for every cached token.
-    ``window`` > 0 means only the last ``window`` tokens are ever read."""
+    ``window`` > 0 means only the last ``window`` tokens are ever read.  ``planes``: 2 for keys
+    and values, 1 for a mixer that keeps one vector per token and head (a latent that is key
+    and value at once)."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2
 
 
 @dataclass(frozen=True)

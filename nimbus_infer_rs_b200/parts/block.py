@@ -21,3 +21,20 @@ class PreNormBlock(Block):
         h = layer.norm_ffn.defer(ctx, x) if ffn.accepts_deferred_norm \
             else layer.norm_ffn.forward(ctx, x)
         ffn.forward(ctx, h, x)
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Block):
+    """``h = norm_mixer(x); x += mixer(h) + ffn(h)``: one norm, both sublayers read its output
+    (the feed-forward may be absent).  Each sublayer adds into the fp32 stream; since neither
+    reads the stream, the order of the two additions only changes the rounding."""
+    graph_safe = True
+
+    def __init__(self):
+        pass
+
+    def forward(self, ctx, x, layer) -> None:
+        h = layer.norm_mixer.forward(ctx, x)
+        layer.mixer.forward(ctx, h, x)
+        if layer.ffn is not None:
+            layer.ffn.forward(ctx, h, x)

@@ -30,3 +30,25 @@ class LayerNorm(Norm):
         out = torch.empty((n, self.width), device=x.device, dtype=ctx.rt.act_dtype)
         ctx.ops.layernorm(x, self.weight, self.bias, self.eps, out, rows)
         return out
+
+
+@register_part("norm", "rmsnorm")
+class RMSNorm(Norm):
+    """``x / sqrt(mean(x^2) + eps) * weight`` per row, statistics and scaling in fp32 (``eps``
+    inside the root).  No kernel folds this norm into the product that follows, so it never
+    defers: one launch gives the rows to every reader."""
+    graph_safe = True
+
+    def __init__(self, width: int, eps: float):
+        self.width = int(width)
+        self.eps = float(eps)
+        self.weight = None
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.width,), VECTOR)}
+
+    def forward(self, ctx, x, rows=None, n_rows=None):
+        n = x.shape[0] if rows is None else (rows.numel() if n_rows is None else n_rows)
+        out = torch.empty((n, self.width), device=x.device, dtype=ctx.rt.act_dtype)
+        ctx.ops.rmsnorm(x, self.weight, self.eps, out, rows)
+        return out

@@ -37,6 +37,112 @@ class CpuBackend:
             y = torch.where((rows[:n] >= 0)[:, None], y, torch.zeros_like(y))
         out.copy_(y.to(out.dtype))
 
+    def rmsnorm(self, x, gamma, eps, out, rows=None, x_col=0):
+        n, d = out.shape
+        src = x[:n] if rows is None else x[rows[:n].long().clamp(min=0)]
+        src = src[:, x_col:x_col + d]
+        y = src / torch.sqrt((src * src).mean(-1, keepdim=True) + eps)
+        if gamma is not None:
+            y = y * gamma
+        if rows is not None:
+            y = torch.where((rows[:n] >= 0)[:, None], y, torch.zeros_like(y))
+        out.copy_(y.to(out.dtype))
+
+    def latent_append(self, src, col, gamma, eps, layout, kv):
+        rank = kv.head_dim
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                continue
+            pos = int(layout.row_pos[r])
+            v = src[r, col:col + rank]
+            v = v / torch.sqrt((v * v).mean() + eps)
+            if gamma is not None:
+                v = v * gamma
+            page = int(kv.block_table[slot, pos // kv.page])
+            kv.k[page, 0, pos % kv.page, :] = v.to(kv.k.dtype)
+
+    def head_linear(self, x, x_col, w, out, layout, gate=None, gate_col=0):
+        n = layout.n_rows
+        n_heads, n_out, n_in = w.shape
+        xs = x[:n, x_col:x_col + n_heads * n_in].float().view(n, n_heads, n_in)
+        y = torch.einsum("rhi,hoi->rho", xs, w.float())
+        if gate is not None:
+            y = y * torch.sigmoid(gate[:n, gate_col:gate_col + n_heads])[:, :, None]
+        y = torch.where((layout.row_slot[:n] >= 0)[:, None, None], y, torch.zeros_like(y))
+        out[:n].copy_(y.reshape(n, n_heads * n_out).to(out.dtype))
+
+    def attention_latent(self, q, layout, kv, n_heads, sink, out, scale, window=0):
+        rank = kv.head_dim
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                out[r].zero_()
+                continue
+            pos = int(layout.row_pos[r])
+            lo = max(0, pos + 1 - window) if window > 0 else 0
+            idx = torch.arange(lo, pos + 1)
+            pages = kv.block_table[slot, (idx // kv.page).long()].long()
+            c = kv.k[pages, 0, (idx % kv.page).long(), :].float()       # [n, rank]
+            a = q[r].float().view(n_heads, rank)
+            s = (a @ c.t()) * scale                                      # [heads, n]
+            m = s.max(-1).values
+            if sink is not None:
+                m = torch.maximum(m, sink)
+            e = torch.exp(s - m[:, None])
+            den = e.sum(-1)
+            if sink is not None:
+                den = den + torch.exp(sink - m)
+            out[r] = ((e / den[:, None]) @ c).reshape(-1).to(out.dtype)
+
+    def moe_route(self, logits, col, n_experts, top, renormalize, layout, idx, weight):
+        n = layout.n_rows
+        s = torch.softmax(logits[:n, col:col + n_experts].float(), dim=-1)
+        order = torch.sort(s, dim=-1, descending=True, stable=True).indices[:, :top]
+        w = torch.gather(s, 1, order)
+        if renormalize:
+            w = w / w.sum(-1, keepdim=True)
+        live = (layout.row_slot[:n] >= 0)[:, None]
+        idx.copy_(torch.where(live, order.to(torch.int32), torch.full_like(idx, -1)))
+        weight.copy_(torch.where(live, w, torch.zeros_like(w)))
+
+    def moe_group(self, idx, n_experts, offsets, order, place):
+        flat = idx.reshape(-1)
+        at = 0
+        place.fill_(-1)
+        for e in range(n_experts):
+            offsets[e] = at
+            for p in torch.nonzero(flat == e).reshape(-1).tolist():
+                order[at] = p
+                place[p] = at
+                at += 1
+        offsets[n_experts] = at
+
+    def moe_linear(self, x, order, row_div, offsets, w, w2, out, act=0):
+        n_experts = w.shape[0]
+        for e in range(n_experts):
+            for at in range(int(offsets[e]), int(offsets[e + 1])):
+                row = int(order[at]) // row_div if order is not None else at
+                v = w[e].float() @ x[row].float()
+                if w2 is not None:
+                    if act == 3:
+                        v = v * torch.sigmoid(v)
+                    elif act == 1:
+                        v = 0.5 * v * (1 + torch.tanh(0.7978845608028654 * (v + 0.044715 * v ** 3)))
+                    elif act == 2:
+                        v = 0.5 * v * (1 + torch.erf(v / math.sqrt(2.0)))
+                    v = v * (w2[e].float() @ x[row].float())
+                out[at] = v.to(out.dtype)
+
+    def moe_combine(self, y, place, weight, residual):
+        n, top = weight.shape
+        pl = place.reshape(-1)
+        for r in range(n):
+            for k in range(top):
+                at = int(pl[r * top + k])
+                if at >= 0:
+                    residual[r] += weight[r, k] * y[at]
+
     def linear(self, x, w, bias, out, act=0, residual=None, norm=None):
         if norm is not None:
             h = torch.empty(x.shape, dtype=norm[3])
