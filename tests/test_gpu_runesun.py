@@ -1,0 +1,174 @@
+"""Runesun on the GPU against the plain implementation, in 32-bit and in bfloat16: whole prompts,
+token by token, portions, unequal batches, slots and pages used again, long decoding, greedy
+generation through the engine's own loop, and inputs made so that a left-out sink or gate, a
+stale cache row or a wrong run order shows."""
+import pytest
+import torch
+
+import plain_runesun as PR
+import runesun_models as RM
+from gpu_helpers import DTYPES, TOL, assert_close
+from nimbus_infer_rs_b200 import Engine, SamplingParams
+
+pytestmark = pytest.mark.gpu
+NAMES = ["P", "Q", "R"]
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("runesun")
+    return {n: RM.make(root, n) for n in RM.CONFIGS}
+
+
+def _tokens(vocab, n, seed):
+    return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def _engine(models, name, dtype, cache_tokens=1024, **kw):
+    return Engine.load(models[name][0], dtype=dtype, cache_tokens=cache_tokens, **kw)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_each_request_alone_and_whole(models, name, dtype):
+    _, cfg, P = models[name]
+    e = _engine(models, name, dtype)
+    for i, n in enumerate((1, 2, 33, 64, 65, 200)):
+        toks = _tokens(cfg["vocab"], n, 10 + i)
+        ref = PR.forward(toks, P, cfg)
+        for again in range(2):                    # the second run of a shape is a replayed graph
+            s = e.alloc_slot()
+            out = e.step([(s, toks, list(range(n)))])
+            e.free_slot(s)
+            assert_close(out, ref, dtype, f"{name} whole, {n} tokens, run {again}")
+    e.check_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_tokens_one_by_one(models, name, dtype):
+    _, cfg, P = models[name]
+    e = _engine(models, name, dtype)
+    for n, head in ((34, 1), (150, 110)):
+        toks = _tokens(cfg["vocab"], n, n)
+        ref = PR.forward(toks, P, cfg)
+        s = e.alloc_slot()
+        outs = [e.step([(s, toks[:head], [head - 1])])]
+        for t in range(head, n):
+            outs.append(e.step([(s, [toks[t]], [0])]))
+        e.free_slot(s)
+        assert_close(torch.cat(outs), ref[head - 1:], dtype, f"{name} from {head} of {n}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["P", "Q"])
+def test_portions_of_several_sizes(models, name, dtype):
+    _, cfg, P = models[name]
+    e = _engine(models, name, dtype)
+    toks = _tokens(cfg["vocab"], 203, 3)
+    ref = PR.forward(toks, P, cfg)
+    s = e.alloc_slot()
+    at, outs = 0, []
+    for size in (2, 61, 1, 2, 64, 3, 70):       # ends on and beside page ends
+        outs.append(e.step([(s, toks[at:at + size], list(range(size)))]))
+        at += size
+    e.free_slot(s)
+    assert_close(torch.cat(outs), ref, dtype, f"{name} portions")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["P", "Q"])
+def test_unequal_batches_on_slots_and_pages_used_again(models, name, dtype):
+    """Batches of unequal prompts, decoded together while the shorter ones end; the cache holds
+    one batch, so the next one gets the same slots and pages with the old rows still in them."""
+    _, cfg, P = models[name]
+    e = _engine(models, name, dtype, cache_tokens=6 * 64, n_slots=3)
+    V = cfg["vocab"]
+    for round_, lens in enumerate(((130, 7, 66), (64, 129, 2), (1, 1, 190))):
+        seqs = [_tokens(V, n, 31 * round_ + i) for i, n in enumerate(lens)]
+        heads = [max(1, n - 3 - 2 * i) for i, n in enumerate(lens)]
+        refs = [PR.forward(t, P, cfg) for t in seqs]
+        slots = [e.alloc_slot() for _ in seqs]
+        out = e.step([(s, t[:h], [0, h - 1]) for s, t, h in zip(slots, seqs, heads)])
+        want = torch.stack([r[j] for r, h in zip(refs, heads) for j in (0, h - 1)])
+        assert_close(out, want, dtype, f"{name} batch {round_} prompts")
+        k = 0
+        while True:
+            live = [i for i in range(3) if heads[i] + k < lens[i]]
+            if not live:
+                break
+            out = e.step([(slots[i], [seqs[i][heads[i] + k]], [0]) for i in live])
+            assert_close(out, torch.stack([refs[i][heads[i] + k] for i in live]), dtype,
+                         f"{name} batch {round_} step {k}")
+            k += 1
+        for s in slots:
+            e.free_slot(s)
+    assert all(g.pool.n_free == g.pool.n_pages for g in e.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_from_the_first_token(models, dtype):
+    _, cfg, P = models["P"]
+    e = _engine(models, "P", dtype)
+    toks = _tokens(257, 260, 9)
+    ref = PR.forward(toks, P, cfg)
+    s = e.alloc_slot()
+    outs = [e.step([(s, [t], [0])]) for t in toks]
+    e.free_slot(s)
+    assert_close(torch.cat(outs), ref, dtype, "260 tokens one by one")
+
+
+def test_greedy_generation_through_the_engines_loop(models):
+    _, cfg, P = models["Q"]
+    e = _engine(models, "Q", "float32", cache_tokens=8 * 64, n_slots=3)
+    prompts = [_tokens(320, n, 70 + n) for n in (5, 63, 1, 120)]
+    out = e.generate(prompts, SamplingParams(max_new_tokens=12, temperature=0.0), max_batch=3)
+    for p, got in zip(prompts, out):
+        assert len(got) == 12
+        ctx = list(p)
+        for step, tok in enumerate(got):
+            logits = PR.forward(ctx, P, cfg)[-1]
+            want = int(torch.argmax(logits))
+            if tok != want:        # only a near tie may differ, and the comparison ends there
+                assert float(logits[want] - logits[tok]) <= 2 * TOL["float32"] * float(logits.abs().max())
+                break
+            ctx.append(tok)
+    assert e.cache.slots.n_free == 3
+
+
+def test_bfloat16_generation_runs_in_a_recorded_decode_session(models):
+    e = _engine(models, "Q", "bfloat16", cache_tokens=8 * 64)
+    prompts = [_tokens(320, n, n) for n in (9, 40)]
+    a = e.generate(prompts, SamplingParams(max_new_tokens=20, temperature=0.0))
+    b = e.generate(prompts, SamplingParams(max_new_tokens=20, temperature=0.0))
+    assert a == b and all(len(x) == 20 for x in a)
+
+
+def test_the_comparison_sees_a_left_out_sink_gate_or_scale(models):
+    """The tests above would not notice a mechanism that changes nothing: leave each out of the
+    plain implementation and see the engine's logits move away by far more than the tolerance."""
+    _, cfg, P = models["P"]
+    e = _engine(models, "P", "float32")
+    toks = _tokens(257, 40, 2)
+    s = e.alloc_slot()
+    out = e.step([(s, toks, list(range(40)))]).double().cpu()
+    e.free_slot(s)
+
+    def moved(Pmod=None, cfgmod=None):
+        ref = PR.forward(toks, Pmod or P, cfgmod or cfg)
+        return float((out - ref).abs().max()) / float(ref.abs().max())
+
+    assert moved() <= TOL["float32"]
+    no_sink = {k: (torch.full_like(v, -1e4) if k.endswith("mix.sink") else v) for k, v in P.items()}
+    assert moved(no_sink) > 1e-2
+    open_gate = {k: (torch.zeros_like(v) if k.endswith("mix.g") else v) for k, v in P.items()}
+    assert moved(open_gate) > 1e-2
+    import copy
+    other_scale = copy.deepcopy(cfg)
+    other_scale["layers"][3]["mixer"]["scale"] = 0.25
+    assert moved(cfgmod=other_scale) > 1e-3
+    not_shared = copy.deepcopy(cfg)
+    del not_shared["layers"][2]["weights_of"]
+    P2 = dict(P, **{k.replace("l1.", "l2."): v for k, v in P.items() if k.startswith("l1.")})
+    not_shared["layers"][2] = copy.deepcopy(cfg["layers"][1])
+    assert moved(P2, not_shared) > 1e-2
