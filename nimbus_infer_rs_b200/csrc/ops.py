@@ -54,6 +54,15 @@ def decode_splits(base_ctas: int, pages: int, page: int, head_dim: int, sms: int
     return s
 
 
+def latent_splits(ctas: int, pages: int, sms: int) -> int:
+    """Into how many runs the tensor-core latent attention cuts the pages of a tile: one when
+    the tiles alone fill the GPU, else as many as bring the launch to about two CTAs per SM,
+    at most one per page and at most 32."""
+    if ctas >= sms or pages < 2:
+        return 1
+    return max(1, min(pages, 32, (2 * sms) // max(1, ctas)))
+
+
 class KernelError(RuntimeError):
     pass
 
@@ -102,6 +111,10 @@ class CudaBackend:
         self._scratch = {}
         self._argmax_scratch = {}
         self._prefill_scr = {}
+        self._latent_scr = {}
+        # NIMBUS_B200_MMA=0 keeps the latent attention and the routed experts' products of a
+        # bfloat16 run on the CUDA-core kernels (comparison runs)
+        self.use_mma = os.environ.get("NIMBUS_B200_MMA", "1") != "0"
         # NIMBUS_B200_NO_TCGEN05=1 keeps large bf16 products on the CUDA-core kernel (debugging)
         self.use_tcgen05 = os.environ.get("NIMBUS_B200_NO_TCGEN05", "") in ("", "0")
         # NIMBUS_B200_STREAM=0 keeps a decode step's products on the kernel that streams weights
@@ -342,7 +355,8 @@ class CudaBackend:
     def scratch_refs(self):
         """The scratch tensors kernels currently use: whoever records launches in a CUDA graph
         keeps these alive with it (growing a scratch buffer replaces the tensor)."""
-        return (dict(self._scratch), dict(self._argmax_scratch), dict(self._prefill_scr))
+        return (dict(self._scratch), dict(self._argmax_scratch), dict(self._prefill_scr),
+                dict(self._latent_scr))
 
     def _prefill_scratch(self, device, n_tiles, max_splits, head_dim):
         """Scratch of the split prefill attention: one record per (tile, split) and one counter
@@ -514,6 +528,33 @@ class CudaBackend:
             _check(sink, "sink", torch.float32, 1)
             if sink.numel() != n_heads:
                 raise KernelError("attention_latent: one sink per head")
+        if self.use_mma and q.dtype == out.dtype == kv.k.dtype == torch.bfloat16 \
+                and self.lib.nb_attention_latent_mma_supported(rank, kv.page, n_heads):
+            # tensor cores: 64 (token, head) pairs a CTA; the pages of a tile are cut into runs
+            # when the launch would leave SMs idle (one-token steps, short prompts)
+            ctas = -(-layout.max_q_len * n_heads // 64) * layout.n_seqs
+            pages = max(1, -(-layout.max_kv_len // kv.page))
+            if window > 0:
+                pages = min(pages, (window + kv.page - 1) // kv.page + 2)
+            n_splits = latent_splits(ctas, pages, self._sms)
+            part_o = part_ml = None
+            if n_splits > 1:
+                need = n * n_heads * n_splits
+                scr = self._latent_scr.get(q.device)
+                if scr is None or scr[1].numel() < need * 2 or scr[0].numel() < need * rank:
+                    scr = (torch.empty(max(need * rank, 1 << 20), dtype=torch.float32, device=q.device),
+                           torch.empty(max(need * 2, 1 << 14), dtype=torch.float32, device=q.device))
+                    self._latent_scr[q.device] = scr
+                part_o, part_ml = scr
+                self.launches += 1          # the merge
+            elif layout.n_rows > layout.n_tokens:
+                out[layout.n_tokens:layout.n_rows].zero_()      # padding rows
+            self._call("nb_attention_latent_mma", _ptr(q), _ptr(layout.cu_rows), _ptr(layout.seq_slot),
+                       _ptr(layout.seq_pos0), _ptr(layout.row_slot), _ptr(kv.k), _ptr(kv.block_table),
+                       kv.block_table.shape[1], kv.page, n_heads, rank, _ptr(sink), _ptr(out), scale,
+                       window, n, layout.n_seqs, layout.max_q_len, n_splits, _ptr(part_o),
+                       _ptr(part_ml), self._stream())
+            return
         self._call("nb_attention_latent", _ptr(q), dtype_code(q.dtype), q.shape[1], 0,
                    _ptr(layout.row_slot), _ptr(layout.row_pos), _ptr(kv.k), dtype_code(kv.k.dtype),
                    _ptr(kv.block_table), kv.block_table.shape[1], kv.page, n_heads, rank,
@@ -558,6 +599,13 @@ class CudaBackend:
                 raise KernelError("moe_linear: the two weight sets differ in shape")
         if x.shape[1] != K or out.shape[1] != N or offsets.numel() < n_experts + 1:
             raise KernelError("moe_linear: shapes do not agree")
+        if self.use_mma and out.dtype in (torch.bfloat16, torch.float32) \
+                and self.lib.nb_moe_gemm_mma_supported(dtype_code(x.dtype), dtype_code(w.dtype),
+                                                       x.shape[1], K):
+            self._call("nb_moe_gemm_mma", _ptr(x), x.shape[1], _ptr(order), row_div, _ptr(offsets),
+                       n_experts, out.shape[0], _ptr(w), _ptr(w2), _ptr(out), dtype_code(out.dtype),
+                       out.shape[1], N, K, act, self._stream())
+            return
         self._call("nb_moe_gemm", _ptr(x), dtype_code(x.dtype), x.shape[1], _ptr(order), row_div,
                    _ptr(offsets), n_experts, out.shape[0], _ptr(w), _ptr(w2), dtype_code(w.dtype),
                    _ptr(out), dtype_code(out.dtype), out.shape[1], N, K, act, self._stream())

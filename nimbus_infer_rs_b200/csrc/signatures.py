@@ -55,6 +55,10 @@ SIGNATURES = {
     "nb_latent_append": "piipfpppipiiiip",
     "nb_head_linear": "piiipipiipiipiiiip",
     "nb_attention_latent": "piiipppipiiiippiifiip",
+    "nb_attention_latent_mma_supported": "iii",
+    "nb_attention_latent_mma": "pppppppiiiippfiiiiippp",
+    "nb_moe_gemm_mma_supported": "iiii",
+    "nb_moe_gemm_mma": "pipipiipppiiiiip",
     "nb_moe_route": "piipiiiippp",
     "nb_moe_group": "piipppp",
     "nb_moe_gemm_tiles": "ii",

@@ -77,9 +77,22 @@ def route(h, P, pre, n_top):
     return s, order
 
 
-def moe(h, P, pre, ff: dict):
+def moe(h, P, pre, ff: dict, told=None, margin=0.0):
+    """``told`` (optional, [T, top]): what another implementation chose.  Where this one's own
+    choice is a close call (the last chosen and the first left-out expert's logits are less than
+    ``margin`` apart) it follows ``told``; everywhere else ``told`` must be its own choice."""
     n_top = ff["router"]["top"]
     s, chosen = route(h, P, pre, n_top)
+    if told is not None:
+        z = torch.sort(h @ P[pre + "router"].T, dim=-1, descending=True).values
+        gap = z[:, n_top - 1] - z[:, n_top] if n_top < z.shape[1] else torch.full((h.shape[0],), math.inf)
+        for t in range(h.shape[0]):
+            mine, theirs = sorted(chosen[t].tolist()), sorted(told[t].tolist())
+            if float(gap[t]) >= margin:
+                assert mine == theirs, f"{pre} token {t}: chose {theirs}, plain says {mine} (gap {float(gap[t]):.3f})"
+            else:
+                assert len(set(theirs)) == n_top and all(0 <= e < s.shape[1] for e in theirs)
+                chosen[t] = torch.tensor(theirs)
     out = torch.zeros(h.shape[0], P[pre + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for e in chosen[t].tolist():
@@ -87,7 +100,7 @@ def moe(h, P, pre, ff: dict):
     return out
 
 
-def layer(x, P, cfg, i):
+def layer(x, P, cfg, i, told=None, margin=0.0):
     entry = cfg["layers"][i]
     src = entry.get("weights_of", i)
     eps = cfg["norm"]["eps"]
@@ -99,18 +112,21 @@ def layer(x, P, cfg, i):
     if entry.get("mlp") is not None:
         if entry["mlp"]["kind"] != "moe":
             raise ValueError(entry["mlp"]["kind"])
-        y = y + moe(h, P, pre + "mlp.", entry["mlp"])
+        y = y + moe(h, P, pre + "mlp.", entry["mlp"], told, margin)
     return x + y
 
 
-def forward(tokens, P, cfg, dtype=torch.float64, keep_layers=False):
+def forward(tokens, P, cfg, dtype=torch.float64, keep_layers=False, routed=None, margin=0.0):
     """Logits at every position of one sequence, ``[T, vocab]`` (and the residual stream after
-    every layer run when ``keep_layers``)."""
+    every layer run when ``keep_layers``).  ``routed``: per layer run with routed experts, in
+    order, the experts another implementation chose ``[T, top]`` (see :func:`moe`)."""
     P = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in P.items()}
     x = P["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     streams = []
+    routed = list(routed) if routed is not None else None
     for i in range(len(cfg["layers"])):
-        x = layer(x, P, cfg, i)
+        told = routed.pop(0) if routed is not None and cfg["layers"][i].get("mlp") is not None else None
+        x = layer(x, P, cfg, i, told, margin)
         streams.append(x)
     logits = rms_norm(x, P["final.norm"], cfg["norm"]["eps"]) @ P["head"].T
     return (logits, torch.stack(streams)) if keep_layers else logits

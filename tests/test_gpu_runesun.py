@@ -28,94 +28,165 @@ def _engine(models, name, dtype, cache_tokens=1024, **kw):
     return Engine.load(models[name][0], dtype=dtype, cache_tokens=cache_tokens, **kw)
 
 
+# A router's choice between two experts whose logits are closer than this is a close call that
+# rounding may settle either way; the plain implementation then follows the engine (and insists
+# on its own choice everywhere else).
+MARGIN = {"float32": 1e-3, "bfloat16": 0.3}
+
+
+class Replay:
+    """Runs steps of ``(request, tokens, want)`` entries through ``Engine.step`` on plain launches
+    and notes, per request, what the router kernel chose at every position of every layer run."""
+
+    def __init__(self, engine):
+        self.e = engine
+        engine.step_graphs = None              # every launch goes through Python: the tap sees it
+        self.slots, self.routed, self._calls = {}, {}, []
+        ops, orig = engine.ops, engine.ops.moe_route
+
+        def tapped(logits, col, n_experts, top, renormalize, layout, idx, weight):
+            orig(logits, col, n_experts, top, renormalize, layout, idx, weight)
+            self._calls.append(idx[:layout.n_tokens].clone())
+        ops.moe_route = tapped
+        self._ops = ops
+
+    def close(self):
+        del self._ops.moe_route                # the class's method is back
+
+    def step(self, entries):
+        for r, _, _ in entries:
+            if r not in self.slots:
+                self.slots[r] = self.e.alloc_slot()
+                self.routed[r] = None
+        out = self.e.step([(self.slots[r], t, w) for r, t, w in entries])
+        calls, self._calls = [c.cpu().long() for c in self._calls], []
+        at = 0
+        for r, t, _ in entries:
+            mine = [c[at:at + len(t)] for c in calls]
+            self.routed[r] = mine if self.routed[r] is None else \
+                [torch.cat([a, b]) for a, b in zip(self.routed[r], mine)]
+            at += len(t)
+        return out
+
+    def end(self, r):
+        self.e.free_slot(self.slots.pop(r))
+
+    def plain(self, r, tokens, P, cfg, dtype):
+        return PR.forward(tokens, P, cfg, routed=self.routed[r], margin=MARGIN[dtype])
+
+
+@pytest.fixture()
+def replay():
+    made = []
+
+    def make(engine):
+        made.append(Replay(engine))
+        return made[-1]
+    yield make
+    for r in made:
+        r.close()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
-def test_each_request_alone_and_whole(models, name, dtype):
+def test_each_request_alone_and_whole(models, replay, name, dtype):
     _, cfg, P = models[name]
-    e = _engine(models, name, dtype)
+    run = replay(_engine(models, name, dtype))
     for i, n in enumerate((1, 2, 33, 64, 65, 200)):
         toks = _tokens(cfg["vocab"], n, 10 + i)
-        ref = PR.forward(toks, P, cfg)
-        for again in range(2):                    # the second run of a shape is a replayed graph
-            s = e.alloc_slot()
-            out = e.step([(s, toks, list(range(n)))])
-            e.free_slot(s)
-            assert_close(out, ref, dtype, f"{name} whole, {n} tokens, run {again}")
-    e.check_errors()
+        out = run.step([(i, toks, list(range(n)))])
+        assert_close(out, run.plain(i, toks, P, cfg, dtype), dtype, f"{name} whole, {n} tokens")
+        run.end(i)
+    run.e.check_errors()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
-def test_last_tokens_one_by_one(models, name, dtype):
+def test_recorded_steps_give_what_plain_launches_give(models, name, dtype):
+    """A step whose shape comes again is replayed from a CUDA graph: bit for bit the same."""
+    _, cfg, _ = models[name]
+    e, plainly = _engine(models, name, dtype), _engine(models, name, dtype)
+    plainly.step_graphs = None
+    for n in (1, 70, 1, 70, 1, 70):
+        toks = _tokens(cfg["vocab"], n, n)
+        s, t = e.alloc_slot(), plainly.alloc_slot()
+        a, b = e.step([(s, toks, list(range(n)))]), plainly.step([(t, toks, list(range(n)))])
+        for k in range(3):
+            a = torch.cat([a, e.step([(s, [k + 1], [0])])])
+            b = torch.cat([b, plainly.step([(t, [k + 1], [0])])])
+        e.free_slot(s)
+        plainly.free_slot(t)
+        assert torch.equal(a, b)
+    assert e.step_graphs.replays > 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_tokens_one_by_one(models, replay, name, dtype):
     _, cfg, P = models[name]
-    e = _engine(models, name, dtype)
+    run = replay(_engine(models, name, dtype))
     for n, head in ((34, 1), (150, 110)):
         toks = _tokens(cfg["vocab"], n, n)
-        ref = PR.forward(toks, P, cfg)
-        s = e.alloc_slot()
-        outs = [e.step([(s, toks[:head], [head - 1])])]
+        outs = [run.step([(n, toks[:head], [head - 1])])]
         for t in range(head, n):
-            outs.append(e.step([(s, [toks[t]], [0])]))
-        e.free_slot(s)
+            outs.append(run.step([(n, [toks[t]], [0])]))
+        ref = run.plain(n, toks, P, cfg, dtype)
+        run.end(n)
         assert_close(torch.cat(outs), ref[head - 1:], dtype, f"{name} from {head} of {n}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["P", "Q"])
-def test_portions_of_several_sizes(models, name, dtype):
+def test_portions_of_several_sizes(models, replay, name, dtype):
     _, cfg, P = models[name]
-    e = _engine(models, name, dtype)
+    run = replay(_engine(models, name, dtype))
     toks = _tokens(cfg["vocab"], 203, 3)
-    ref = PR.forward(toks, P, cfg)
-    s = e.alloc_slot()
     at, outs = 0, []
     for size in (2, 61, 1, 2, 64, 3, 70):       # ends on and beside page ends
-        outs.append(e.step([(s, toks[at:at + size], list(range(size)))]))
+        outs.append(run.step([(0, toks[at:at + size], list(range(size)))]))
         at += size
-    e.free_slot(s)
-    assert_close(torch.cat(outs), ref, dtype, f"{name} portions")
+    assert_close(torch.cat(outs), run.plain(0, toks, P, cfg, dtype), dtype, f"{name} portions")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["P", "Q"])
-def test_unequal_batches_on_slots_and_pages_used_again(models, name, dtype):
+def test_unequal_batches_on_slots_and_pages_used_again(models, replay, name, dtype):
     """Batches of unequal prompts, decoded together while the shorter ones end; the cache holds
     one batch, so the next one gets the same slots and pages with the old rows still in them."""
     _, cfg, P = models[name]
-    e = _engine(models, name, dtype, cache_tokens=6 * 64, n_slots=3)
-    V = cfg["vocab"]
+    run = replay(_engine(models, name, dtype, cache_tokens=6 * 64, n_slots=3))
+    e, V = run.e, cfg["vocab"]
     for round_, lens in enumerate(((130, 7, 66), (64, 129, 2), (1, 1, 190))):
         seqs = [_tokens(V, n, 31 * round_ + i) for i, n in enumerate(lens)]
         heads = [max(1, n - 3 - 2 * i) for i, n in enumerate(lens)]
-        refs = [PR.forward(t, P, cfg) for t in seqs]
-        slots = [e.alloc_slot() for _ in seqs]
-        out = e.step([(s, t[:h], [0, h - 1]) for s, t, h in zip(slots, seqs, heads)])
-        want = torch.stack([r[j] for r, h in zip(refs, heads) for j in (0, h - 1)])
-        assert_close(out, want, dtype, f"{name} batch {round_} prompts")
+        got = {i: [] for i in range(3)}
+        out = run.step([(i, t[:h], [0, h - 1]) for i, (t, h) in enumerate(zip(seqs, heads))])
+        for i in range(3):
+            got[i] += [out[2 * i], out[2 * i + 1]]
         k = 0
         while True:
             live = [i for i in range(3) if heads[i] + k < lens[i]]
             if not live:
                 break
-            out = e.step([(slots[i], [seqs[i][heads[i] + k]], [0]) for i in live])
-            assert_close(out, torch.stack([refs[i][heads[i] + k] for i in live]), dtype,
-                         f"{name} batch {round_} step {k}")
+            out = run.step([(i, [seqs[i][heads[i] + k]], [0]) for i in live])
+            for j, i in enumerate(live):
+                got[i].append(out[j])
             k += 1
-        for s in slots:
-            e.free_slot(s)
+        for i in range(3):
+            ref = run.plain(i, seqs[i], P, cfg, dtype)
+            places = [0, heads[i] - 1] + list(range(heads[i], lens[i]))
+            assert_close(torch.stack(got[i]), ref[places], dtype, f"{name} batch {round_} request {i}")
+            run.end(i)
     assert all(g.pool.n_free == g.pool.n_pages for g in e.cache.groups)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding_from_the_first_token(models, dtype):
+def test_long_decoding_from_the_first_token(models, replay, dtype):
     _, cfg, P = models["P"]
-    e = _engine(models, "P", dtype)
+    run = replay(_engine(models, "P", dtype))
     toks = _tokens(257, 260, 9)
-    ref = PR.forward(toks, P, cfg)
-    s = e.alloc_slot()
-    outs = [e.step([(s, [t], [0])]) for t in toks]
-    e.free_slot(s)
-    assert_close(torch.cat(outs), ref, dtype, "260 tokens one by one")
+    outs = [run.step([(0, [t], [0])]) for t in toks]
+    assert_close(torch.cat(outs), run.plain(0, toks, P, cfg, dtype), dtype, "260 tokens one by one")
 
 
 def test_greedy_generation_through_the_engines_loop(models):
