@@ -19,6 +19,13 @@ events around exactly K captured steps), ``e2e`` = the same through the Python e
   end-to-end tokens per second, bytes per step and their fraction of the copy bandwidth;
 * ``clocks`` and ``gpu_launches``.
 
+``python bench.py --designs`` is another measurement with a line of its own (the default
+workload and its line stay as they are): the Runesun design (latent attention, routed experts)
+beside GPT-2 at equal layer sizes (presets ``runesun-2k`` / ``gpt2-2k`` and ``runesun-1k`` /
+``gpt2-1k``, random weights): decode steps at batch 8 and 64 and a 2 x 1024-token prefill, and
+per kind of kernel the time inside a plainly launched step with its bytes, flops and fraction of
+the measured roofline.
+
 Every decode step reads all weights (247 MB in bf16) and the cache of the live requests,
 far more than the 126 MB L2, so no L2 flush is needed between timed steps.  Model sizes come
 from the package's presets (config files), none stands here.
@@ -279,6 +286,186 @@ def run_workload(engine, cfg, prompt_lens, n_new, hbm_gbs, windows=()):
     return res
 
 
+# ---------------------------------------------------------------------------------------------
+# --designs: Runesun beside GPT-2 at equal layer sizes
+# ---------------------------------------------------------------------------------------------
+DESIGN_PAIRS = (("runesun-2k", "gpt2-2k"), ("runesun-1k", "gpt2-1k"))
+
+
+class OpTimer:
+    """Times every call into the kernel library during plainly launched steps (CUDA events on
+    the stream around each call) and notes the bytes a call has to move and its flops, from the
+    tensors it is given.  Kernels of a kind are added up."""
+
+    KINDS = ("linear", "layernorm", "rmsnorm", "attention", "attention_latent", "latent_append",
+             "head_linear", "moe_route", "moe_group", "moe_linear", "moe_combine", "embed_pos")
+
+    def __init__(self, ops):
+        import torch
+        self.torch, self.ops, self.records, self._orig = torch, ops, [], {}
+        # written before every timed call: it empties the L2 (larger than its 126 MB), and while
+        # the GPU is busy with it the host gets the call's launches queued, so that the events
+        # see the kernels' time and not the host's
+        self.flush = torch.empty(256 << 20, dtype=torch.int8, device="cuda")
+        for kind in self.KINDS:
+            if hasattr(ops, kind):
+                self._orig[kind] = getattr(ops, kind)
+                setattr(ops, kind, self._wrap(kind, self._orig[kind]))
+
+    def close(self):
+        for kind in self._orig:
+            delattr(self.ops, kind)
+
+    def _wrap(self, kind, fn):
+        torch = self.torch
+
+        def call(*a, **kw):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.flush.zero_()
+            t0.record()
+            fn(*a, **kw)
+            t1.record()
+            self.records.append((kind, self._label(kind, a, kw), t0, t1, *self._work(kind, a, kw)))
+        return call
+
+    @staticmethod
+    def _nbytes(*ts):
+        return sum(t.numel() * t.element_size() for t in ts if t is not None)
+
+    def _label(self, kind, a, kw):
+        if kind == "linear":
+            return f"linear {a[1].shape[0]}x{a[1].shape[1]}"
+        if kind == "moe_linear":
+            return "moe_linear gate+up" if a[5] is not None else "moe_linear down"
+        return kind
+
+    def _work(self, kind, a, kw):
+        """(bytes, flops) of one call."""
+        nb = self._nbytes
+        if kind == "linear":
+            x, w, bias, out = a[0], a[1], a[2], a[3]
+            return nb(w, out) + x.shape[0] * w.shape[1] * w.element_size(), 2 * x.shape[0] * w.shape[0] * w.shape[1]
+        if kind in ("attention", "attention_latent"):
+            if kind == "attention":
+                q, lay, kv, heads = a[0], a[2], a[3], a[4]
+                per_key, planes = kv.n_kv_heads * kv.head_dim, 2
+                width = heads * kv.head_dim
+            else:
+                q, lay, kv, heads = a[0], a[1], a[2], a[3]
+                per_key, planes = kv.head_dim, 1
+                width = heads * kv.head_dim
+            elt = kv.k.element_size()
+            keys = sum(p + n for p, n in zip(lay.seq_pos0_host, lay.seq_lens))
+            pairs = sum(n * p + n * (n + 1) // 2 for p, n in zip(lay.seq_pos0_host, lay.seq_lens))
+            return keys * per_key * planes * elt + 2 * lay.n_tokens * width * elt, 4 * pairs * width
+        if kind == "head_linear":
+            x, w, out, lay = a[0], a[2], a[3], a[4]
+            return nb(w, out) + lay.n_rows * w.shape[0] * w.shape[2] * x.element_size(), \
+                2 * lay.n_rows * w.shape[0] * w.shape[1] * w.shape[2]
+        if kind == "moe_linear":
+            x, offsets, w, w2, out = a[0], a[3], a[4], a[5], a[6]
+            off = offsets.cpu()
+            used = int(((off[1:] - off[:-1]) > 0).sum())
+            sets = 2 if w2 is not None else 1
+            pairs = int(off[-1])
+            return used * sets * w.shape[1] * w.shape[2] * w.element_size() + nb(out) + \
+                pairs * w.shape[2] * x.element_size(), 2 * pairs * sets * w.shape[1] * w.shape[2]
+        if kind in ("layernorm", "rmsnorm"):
+            out = a[4] if kind == "layernorm" else a[3]
+            return 4 * out.numel() + nb(out), 0
+        if kind == "moe_combine":
+            return nb(a[0]) + 2 * nb(a[3]), 0
+        return 0, 0
+
+    def table(self, peaks):
+        self.torch.cuda.synchronize()
+        rows = {}
+        for kind, label, t0, t1, nbytes, flops in self.records:
+            r = rows.setdefault(label, {"calls": 0, "ms": 0.0, "bytes": 0, "flops": 0})
+            r["calls"] += 1
+            r["ms"] += t0.elapsed_time(t1)
+            r["bytes"] += nbytes
+            r["flops"] += flops
+        for r in rows.values():
+            ideal_ms = max(r["bytes"] / (peaks["hbm_gbs"] * 1e6), r["flops"] / (peaks["bf16_tflops"] * 1e9))
+            r["us_per_call"] = round(1e3 * r["ms"] / r["calls"], 2)
+            r["of_roofline"] = round(ideal_ms / r["ms"], 4) if r["ms"] > 0 and ideal_ms > 0 else None
+            r["bound"] = "hbm" if r["bytes"] / (peaks["hbm_gbs"] * 1e6) >= r["flops"] / (peaks["bf16_tflops"] * 1e9) else "tensor"
+            r["ms"] = round(r["ms"], 4)
+        self.records = []
+        return rows
+
+
+def profile_ops(engine, peaks, batch, context, prefill):
+    """Per kind of kernel: a decode step of `batch` sequences at `context`, and a prompt step of
+    `prefill` = (sequences, length), both launched plainly with events around every call."""
+    import torch
+    V = engine.spec.vocab_size
+    graphs, engine.step_graphs = engine.step_graphs, None
+    timer = OpTimer(engine.ops)
+    out = {}
+    try:
+        slots = [engine.alloc_slot() for _ in range(batch)]
+        for i in range(0, batch, 16):
+            engine.step([(s, p, []) for s, p in zip(slots[i:i + 16], prompts_for(len(slots[i:i + 16]), context - 4, V, 5))])
+        for _ in range(2):
+            engine.step([(s, [1], [0]) for s in slots])
+        timer.records = []
+        torch.cuda.synchronize()
+        engine.step([(s, [1], [0]) for s in slots])
+        out["decode"] = timer.table(peaks)
+        for s in slots:
+            engine.free_slot(s)
+        n_seqs, length = prefill
+        for rep in range(2):
+            slots = [engine.alloc_slot() for _ in range(n_seqs)]
+            timer.records = []
+            torch.cuda.synchronize()
+            engine.step([(s, p, [length - 1]) for s, p in zip(slots, prompts_for(n_seqs, length, V, 6 + rep))])
+            table = timer.table(peaks)
+            for s in slots:
+                engine.free_slot(s)
+        out["prefill"] = table
+    finally:
+        timer.close()
+        engine.step_graphs = graphs
+    return out
+
+
+def compare_designs(args, peaks):
+    import torch
+    from nimbus_infer_rs_b200 import Engine
+    results = []
+    launches = 0
+    with ClockSampler() as clocks:
+        for pair in DESIGN_PAIRS:
+            entry = {}
+            for name in pair:
+                engine = Engine.random(name, seed=0, dtype="bfloat16", cache_tokens=66 * CONTEXT)
+                r = {"weight_mb": round(engine.model.weight_bytes() / 2 ** 20, 1)}
+                for batch in (8, 64):
+                    ms, n, _ = time_decode(engine, batch, CONTEXT, args.steps, args.warmup)
+                    launches += n
+                    r[f"decode_b{batch}_ms"] = round(ms, 4)
+                    r[f"decode_b{batch}_tok_s"] = round(batch / (ms * 1e-3), 1)
+                pre = time_prefill(engine, PREFILL_TOKENS // CONTEXT, CONTEXT, reps=5)
+                r["prefill_2x1024_ms"] = round(pre["median"], 4)
+                r["prefill_tok_s"] = round(PREFILL_TOKENS / (pre["median"] * 1e-3), 1)
+                r["kernels"] = profile_ops(engine, peaks, 8, CONTEXT, (PREFILL_TOKENS // CONTEXT, CONTEXT))
+                entry[name] = r
+                del engine
+                torch.cuda.empty_cache()
+            results.append(entry)
+    print(json.dumps({"designs": results, "dtype": "bf16", "data": "synthetic", "steps": args.steps,
+                      "warmup": args.warmup, "gpu_launches": launches, "clocks": clocks.summary(),
+                      "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops")},
+                      "config": {"decode_context": CONTEXT, "prefill": "2 x 1024 tokens",
+                                 "l2": "decode and prefill steps read the model's weights, larger "
+                                       "than L2; the per-kernel profile writes 256 MB before every "
+                                       "timed call"}}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -295,6 +482,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only decode: context the steps end at")
     ap.add_argument("--model", default=MODEL, choices=[MODEL, *OTHER_MODELS],
                     help="layer sizes (a preset); other than the default only with --only")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the headline: Runesun beside GPT-2 at equal layer sizes "
+                         "(decode, prefill, per-kernel roofline fractions)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -314,6 +504,8 @@ def main() -> int:
     from nimbus_infer_rs_b200.config import load_preset
 
     peaks = load_peaks()
+    if args.designs:
+        return compare_designs(args, peaks)
     dtype = "bfloat16" if args.dtype == "bf16" else "float32"
     if args.model != MODEL and args.only == "all":
         print("--model other than gpt2 needs --only decode or --only prefill")

@@ -148,6 +148,19 @@ class RunesunConfig:
             i = self.layers[i].weights_of
         return i
 
+    def n_params(self, *_unused) -> int:
+        """Parameters of the layers that have tensors of their own, the embedding and the head."""
+        total = 2 * self.vocab_size * self.width + self.width
+        for i, l in enumerate(self.layers):
+            if l.weights_of is not None:
+                continue
+            m, D = l.mixer, self.width
+            total += D + m.heads * m.dim * D + m.kv_rank * D + m.kv_rank + m.heads * m.dim * m.kv_rank \
+                + m.heads * m.vdim * m.kv_rank + m.heads + m.heads * D + D * m.heads * m.vdim
+            if l.mlp is not None:
+                total += l.mlp.experts * (3 * l.mlp.ff * D + D)
+        return total
+
     def to_json(self) -> dict[str, Any]:
         out = []
         for l in self.layers:

@@ -507,6 +507,12 @@ class CudaBackend:
             _check(gate, "gate", torch.float32, 2)
             if gate.shape[0] < n or gate.shape[1] < gate_col + n_heads:
                 raise KernelError("head_linear: gate shape does not match")
+        if self.use_mma and self.lib.nb_head_linear_mma_supported(
+                dtype_code(x.dtype), dtype_code(w.dtype), dtype_code(out.dtype), x.shape[1], x_col, n_in):
+            self._call("nb_head_linear_mma", _ptr(x), dtype_code(x.dtype), x.shape[1], x_col, _ptr(w),
+                       _ptr(out), out.shape[1], _ptr(gate), gate.shape[1] if gate is not None else 0,
+                       gate_col, _ptr(layout.row_slot), n, n_heads, n_in, n_out, self._stream())
+            return
         self._call("nb_head_linear", _ptr(x), dtype_code(x.dtype), x.shape[1], x_col, _ptr(w),
                    dtype_code(w.dtype), _ptr(out), dtype_code(out.dtype), out.shape[1], _ptr(gate),
                    gate.shape[1] if gate is not None else 0, gate_col, _ptr(layout.row_slot), n,

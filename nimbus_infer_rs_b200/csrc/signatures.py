@@ -59,6 +59,8 @@ SIGNATURES = {
     "nb_attention_latent_mma": "pppppppiiiippfiiiiippp",
     "nb_moe_gemm_mma_supported": "iiii",
     "nb_moe_gemm_mma": "pipipiipppiiiiip",
+    "nb_head_linear_mma_supported": "iiiiii",
+    "nb_head_linear_mma": "piiippipiipiiiip",
     "nb_moe_route": "piipiiiippp",
     "nb_moe_group": "piipppp",
     "nb_moe_gemm_tiles": "ii",

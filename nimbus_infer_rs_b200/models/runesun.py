@@ -103,16 +103,18 @@ def weight_plan(cfg: RunesunConfig, spec: ModelSpec, names: set[str]) -> WeightP
     return WeightPlan(r, set())
 
 
-def random_tensors(cfg: RunesunConfig, seed: int, *, gain: float = 1.0, sink_std: float = 1.0,
-                   gamma_jitter: float = 0.1, dtype: torch.dtype = torch.bfloat16) -> dict:
-    """Random Runesun tensors under the names of a weight file.  Matrices ~N(0, gain^2 / in),
-    embeddings ~N(0, 1), norm weights 1 + N(0, gamma_jitter^2), sinks ~N(0, sink_std^2); drawn
-    in fp32 from a seeded CPU generator in a fixed order and stored in ``dtype``."""
+def random_tensors(cfg: RunesunConfig, seed: int, *, gain: float = 1.0, std: float | None = None,
+                   sink_std: float = 1.0, gamma_jitter: float = 0.1,
+                   dtype: torch.dtype = torch.bfloat16) -> dict:
+    """Random Runesun tensors under the names of a weight file.  Matrices ~N(0, gain^2 / in) (or
+    ~N(0, std^2) if ``std`` is given), embeddings ~N(0, 1), norm weights 1 + N(0,
+    gamma_jitter^2), sinks ~N(0, sink_std^2); drawn in fp32 from a seeded CPU generator in a
+    fixed order and stored in ``dtype``."""
     g = torch.Generator(device="cpu")
     g.manual_seed(int(seed))
 
     def mat(n_out, n_in, s=None):
-        s = gain / math.sqrt(n_in) if s is None else s
+        s = (gain / math.sqrt(n_in) if std is None else std) if s is None else s
         return (torch.randn(n_out, n_in, generator=g, dtype=torch.float32) * s).to(dtype)
 
     def vec(n, s, mean=0.0):

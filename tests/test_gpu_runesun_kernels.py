@@ -220,6 +220,30 @@ def test_per_head_linear_with_gate(ops, dt):
             (2e-5 if dt == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("x_dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mma", [False, True])
+def test_per_head_linear_on_the_tensor_cores(ops, x_dt, mma):
+    """bf16 weights and results, rows in 32-bit (a slice of a wider 32-bit matrix) or bf16; sizes
+    with ragged tiles; padding rows give zeros whatever their inputs hold."""
+    for H, n_in, n_out, rows in ((2, 8, 8, 1), (5, 24, 72, 67), (16, 128, 256, 130), (3, 256, 40, 9)):
+        lay = build_layout([(1, [0] * rows, [])], [0], DEV, pad_rows_to=8)
+        x = _rnd(lay.n_rows, 16 + H * n_in, seed=1).to(x_dt)
+        x[rows:] = float("nan")
+        w = _rnd(H, n_out, n_in, seed=2, s=1 / math.sqrt(n_in)).to(torch.bfloat16)
+        gate = _rnd(lay.n_rows, H + 3, seed=3)
+        out = torch.full((lay.n_rows, H * n_out), float("nan"), dtype=torch.bfloat16, device=DEV)
+        was = ops.use_mma
+        ops.use_mma = mma
+        try:
+            ops.head_linear(x.to(DEV), 16, w.to(DEV), out, lay, gate=gate.to(DEV), gate_col=2)
+        finally:
+            ops.use_mma = was
+        xs = x[:rows, 16:].to(torch.bfloat16).double().view(rows, H, n_in)
+        ref = torch.einsum("rhi,hoi->rho", xs, w.double()) * torch.sigmoid(gate[:rows, 2:2 + H].double())[:, :, None]
+        assert _rel(out[:rows].view(rows, H, n_out), ref) < 1e-2
+        assert (out[rows:] == 0).all()
+
+
 def test_router_choice_order_ties_and_weights(ops):
     lay = build_layout([(1, [0] * 5, [])], [0], DEV, pad_rows_to=8)
     E, top = 7, 3

@@ -164,3 +164,47 @@ def test_random_weights_mode_and_inspect(cpu_backend):
     assert info["architecture"] == "runesun" and info["mixer"] == "latent_attention"
     assert info["ffn"] == "routed_experts" and info["norm"] == "rmsnorm" and info["pos"] == "none"
     json.dumps(info)
+
+
+def test_command_line_and_trace_replay_take_the_design(cpu_backend, tmp_path, monkeypatch, capsys):
+    """`random` writes a model folder of the preset; `logits` and trace replay read it back
+    through the registry like any other model."""
+    import importlib.machinery
+    import importlib.util
+    import io
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    from nimbus_infer_rs_b200.__main__ import main
+    folder = tmp_path / "m"
+    assert main(["random", "--out", str(folder), "--preset", "runesun-tiny", "--seed", "3"]) == 0
+    wrote = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    cfg = json.loads((folder / "config.json").read_text())
+    assert cfg["architecture"] == "Runesun" and cfg["layers"][2]["weights_of"] == 0
+    e = Engine.load(folder, dtype="float32", device="cpu", cache_tokens=128)
+    assert wrote["n_params"] == e.model.n_params()
+
+    root = Path(__file__).resolve().parent.parent
+    loader = importlib.machinery.SourceFileLoader("trace_run_program", str(root / "bin" / "trace_run"))
+    mod = importlib.util.module_from_spec(importlib.util.spec_from_loader(loader.name, loader))
+    loader.exec_module(mod)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3, 4], "want": [1, 3]},
+                                     {"id": "b", "tokens": [9], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": [5], "want": [0]},
+                                     {"id": "b", "tokens": [8], "want": [0]}], "end": ["a", "b"]}]
+    out = tmp_path / "out"
+    monkeypatch.setattr(sys, "argv", ["trace_run", "--model", str(folder), "--dtype", "float32", "--out",
+                                      str(out), "--max-tokens", "128", "--device", "cpu"])
+    monkeypatch.setattr(sys, "stdin", io.StringIO("".join(json.dumps(s) + "\n" for s in steps)))
+    assert mod.main() == 0
+    assert [l for l in capsys.readouterr().out.split("\n") if l] == ["done 0", "done 1"]
+    from nimbus_infer_rs_b200.weights.safetensors_io import SafeTensorsFile
+    with SafeTensorsFile(folder / "model.safetensors") as f:
+        P = {n: f.tensor(n).float() for n in f.names()}
+    a, b = PR.forward([1, 2, 3, 4, 5], P, cfg), PR.forward([9, 8], P, cfg)
+    got0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1))
+    got1 = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(2, -1))
+    _close(got0, a[[1, 3]])
+    _close(got1, torch.stack([a[4], b[1]]))
