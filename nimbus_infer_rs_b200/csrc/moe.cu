@@ -217,7 +217,7 @@ __global__ void moe_combine_kernel(const float* y, int width, const int* place, 
   nb_grid_dependency_wait();
   nb_launch_dependents();
   const int r = blockIdx.x;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < width; i += gridDim.y * blockDim.x) {
     float s = 0.0f;
     for (int k = 0; k < top; ++k) {
       const int at = place[(size_t)r * top + k];
@@ -305,9 +305,12 @@ NB_EXPORT int nb_moe_combine(const float* y, int width, const int* place, const 
                              int top, float* residual, int n_rows, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NB_REQUIRE(width > 0 && top >= 1, NB_ERR_BAD_ARG, "moe_combine: bad sizes");
-  const int threads = width >= 1024 ? 256 : 128;
-  NB_CUDA(nb_launch(moe_combine_kernel, dim3(n_rows), dim3(threads), 0, stream, y, width, place,
-                    weight, top, residual));
+  // a thread per element of the stream while the launch stays small; rows of a long prompt
+  // walk over their width instead
+  const int threads = 128;
+  const int chunks = n_rows <= 256 ? (width + threads - 1) / threads : (width + 4 * threads - 1) / (4 * threads);
+  NB_CUDA(nb_launch(moe_combine_kernel, dim3(n_rows, chunks), dim3(threads), 0, stream, y, width,
+                    place, weight, top, residual));
   NB_CHECK_LAUNCH("moe_combine");
   return 0;
 }

@@ -16,18 +16,22 @@ import plain_gpt2 as P
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _main():
+def _program():
     loader = importlib.machinery.SourceFileLoader("trace_run_program", str(ROOT / "bin" / "trace_run"))
     spec = importlib.util.spec_from_loader(loader.name, loader)
     mod = importlib.util.module_from_spec(spec)
     loader.exec_module(mod)
-    return mod.main
+    return mod
 
 
-def _run(monkeypatch, capsys, argv, steps):
+def _run(monkeypatch, capsys, argv, steps, part_pages=0):
+    """``part_pages``: for how many live requests' partly used pages the cache gets room on top
+    of --max-tokens (the program's default is generous; 0 makes the cache exactly that large)."""
     monkeypatch.setattr(sys, "argv", ["trace_run", *argv, "--device", "cpu"])
     monkeypatch.setattr(sys, "stdin", io.StringIO("".join(json.dumps(s) + "\n" for s in steps) + "\n"))
-    assert _main()() == 0
+    mod = _program()
+    mod.LIVE_REQUESTS_ROOM = part_pages
+    assert mod.main() == 0
     return capsys.readouterr().out.split("\n")
 
 
@@ -89,3 +93,9 @@ def test_more_live_tokens_than_max_tokens_is_an_error_not_a_wrong_answer(cpu_bac
         _run(monkeypatch, capsys, ["--random", "tiny-b", "--dtype", "float32", "--out",
                                    str(tmp_path / "o"), "--max-tokens", "64"], steps)
     assert not (tmp_path / "o" / "0.f32").exists()
+    # --max-tokens counts tokens, not pages: with the program's own room for part pages, three
+    # tokens in two requests are well within 64
+    lines = _run(monkeypatch, capsys, ["--random", "tiny-b", "--dtype", "float32", "--out",
+                                       str(tmp_path / "q"), "--max-tokens", "64"], steps, part_pages=256)
+    assert "done 0" in lines and (tmp_path / "q" / "0.f32").exists()
+    assert _program().cache_tokens_for(64) == 64 + 64 * 64 and _program().cache_tokens_for(1000) == 1024 + 64 * 256
