@@ -67,6 +67,9 @@ moe_mma_kernel(const TX* x, int x_stride, const int* order, int row_div, const i
   __syncthreads();
   x += (size_t)e * x_gcol;
   y += (size_t)e * y_gcol;
+  // 32-bit rows can be fetched 16 bytes at a time when every row's piece starts on such a boundary
+  const bool x_vec4 = sizeof(TX) == 4 && x_stride % 4 == 0 && x_gcol % 4 == 0 &&
+                      (reinterpret_cast<uintptr_t>(x) & 15) == 0;
   const bf16* We = W + (size_t)e * N * K;
   const bf16* We2 = DUAL ? W2 + (size_t)e * N * K : nullptr;
 
@@ -79,7 +82,26 @@ moe_mma_kernel(const TX* x, int x_stride, const int* order, int row_div, const i
         cp_async16_zfill(As + (stage * BM + rr) * LD + (i & 7) * 8,
                          ok ? x + (size_t)src * x_stride + k : x, ok);
       }
-    } else {   // 32-bit rows: rounded to bf16 on the way into shared memory
+    } else if (x_vec4) {   // 32-bit rows: rounded to bf16 on the way into shared memory
+      constexpr int PER = BM * BK / 4 / THREADS;
+      float4 v[PER];
+#pragma unroll
+      for (int u = 0; u < PER; ++u) {      // all loads first, then the stores
+        const int i = tid + u * THREADS, rr = i / (BK / 4), k = k0 + (i % (BK / 4)) * 4;
+        const int src = a_row[rr];
+        v[u] = (src >= 0 && k < K)
+                   ? *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + (size_t)src * x_stride + k)
+                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+#pragma unroll
+      for (int u = 0; u < PER; ++u) {
+        const int i = tid + u * THREADS, rr = i / (BK / 4), kk = (i % (BK / 4)) * 4;
+        uint2 pk;
+        pk.x = pack_bf16(v[u].x, v[u].y);
+        pk.y = pack_bf16(v[u].z, v[u].w);
+        *reinterpret_cast<uint2*>(As + (stage * BM + rr) * LD + kk) = pk;
+      }
+    } else {
       for (int i = tid; i < BM * BK; i += THREADS) {
         const int rr = i / BK, kk = i % BK;
         const int src = a_row[rr];

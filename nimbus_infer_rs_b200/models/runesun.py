@@ -53,14 +53,19 @@ def build_spec(cfg: RunesunConfig) -> ModelSpec:
         schedule=schedule)
 
 
-def _rows(names_shapes) -> Recipe:
-    """Several ``(out_i, in)`` matrices, one under the other."""
+def _rows(names_shapes, multiple: int = 1) -> Recipe:
+    """Several ``(out_i, in)`` matrices, one under the other, then rows of zeros up to a
+    multiple of ``multiple`` rows."""
     srcs = [Source(n, (tuple(s),)) for n, s in names_shapes]
 
     def combine(ts):
         kinds = {t.dtype for t in ts}
         if len(kinds) > 1:
             ts = [t.to(torch.float32) for t in ts]
+        rows = sum(t.shape[0] for t in ts)
+        pad = -rows % multiple
+        if pad:
+            ts = list(ts) + [torch.zeros((pad, ts[0].shape[1]), dtype=ts[0].dtype)]
         return torch.cat(list(ts), dim=0).contiguous()
     return Recipe(srcs, combine)
 
@@ -84,7 +89,7 @@ def weight_plan(cfg: RunesunConfig, spec: ModelSpec, names: set[str]) -> WeightP
         fused = [(p + "mix.q", (H * d, D)), (p + "mix.dkv", (R, D)), (p + "mix.g", (H, D))]
         if ff is not None:
             fused.append((p + "mlp.router", (ff.experts, D)))
-        r[L + "mixer.proj.weight"] = _rows(fused)
+        r[L + "mixer.proj.weight"] = _rows(fused, multiple=8)
         r[L + "mixer.latent_norm"] = take(p + "mix.dkv.norm", (R,))
         # stored [H*d, R]: head i's rows map the latent to its keys; held transposed per head
         r[L + "mixer.key_up"] = Recipe(

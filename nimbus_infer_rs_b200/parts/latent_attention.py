@@ -41,7 +41,10 @@ class LatentAttention(Mixer):
         self.col_latent = self.q_width
         self.col_gate = self.col_latent + self.latent_dim
         self.col_extra = self.col_gate + (self.n_heads if self.has_gate else 0)
-        self.proj = Linear(self.width, self.col_extra + self.extra_outputs, bias=False)
+        # rows of zeros fill the projection up to a multiple of 8 outputs, so that its fp32 rows
+        # start on 32-byte boundaries whatever the numbers of heads and extra outputs are
+        self.proj_outputs = -(-(self.col_extra + self.extra_outputs) // 8) * 8
+        self.proj = Linear(self.width, self.proj_outputs, bias=False)
         self.out = Linear(self.n_heads * self.value_dim, self.width, bias=False)
         self.latent_norm = self.key_up = self.value_up = self.sink = None
 

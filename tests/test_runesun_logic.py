@@ -183,8 +183,10 @@ def test_command_line_and_trace_replay_take_the_design(cpu_backend, tmp_path, mo
     wrote = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     cfg = json.loads((folder / "config.json").read_text())
     assert cfg["architecture"] == "Runesun" and cfg["layers"][2]["weights_of"] == 0
-    e = Engine.load(folder, dtype="float32", device="cpu", cache_tokens=128)
-    assert wrote["n_params"] == e.model.n_params()
+    from nimbus_infer_rs_b200.weights.safetensors_io import SafeTensorsFile
+    with SafeTensorsFile(folder / "model.safetensors") as f:
+        assert wrote["n_params"] == sum(f.tensor(n).numel() for n in f.names())
+    Engine.load(folder, dtype="float32", device="cpu", cache_tokens=128)
 
     root = Path(__file__).resolve().parent.parent
     loader = importlib.machinery.SourceFileLoader("trace_run_program", str(root / "bin" / "trace_run"))
