@@ -31,6 +31,7 @@ FUSED_NORM_MAX_COLS = 16384    # ... and output columns (a long weight stream wa
 SKINNY_MAX_ROWS = 64   # matrix products with at most this many rows take the weight-streaming kernel
 STREAM_MAX_ROWS = 16   # ... and with at most this many the kernel that stages weights in shared memory
 ROWS_MAX_ROWS = 128    # up to this many rows a product's weights are the tensor cores' 128-row operand
+MOE_TC_MIN_PLACES = 1024   # from this many (token, choice) pairs on the experts' products take tcgen05 tiles
 
 
 def decode_splits(base_ctas: int, pages: int, page: int, head_dim: int, sms: int, most: int) -> int:
@@ -314,7 +315,8 @@ class CudaBackend:
         kernel gives up and reports it (``None``: the default, about two seconds)."""
         cycles = 4_000_000_000 if cycles is None else int(cycles)
         for fn in ("nb_gemm_tcgen05_set_wait_budget", "nb_attention_prefill_tc_set_wait_budget",
-                   "nb_gemm_stream_set_wait_budget", "nb_gemm_tc_rows_set_wait_budget"):
+                   "nb_gemm_stream_set_wait_budget", "nb_gemm_tc_rows_set_wait_budget",
+                   "nb_moe_gemm_tc_set_wait_budget"):
             rc = getattr(self.lib, fn)(cycles)
             if rc != 0:
                 raise KernelError(f"{fn} failed ({rc}): "
@@ -605,6 +607,22 @@ class CudaBackend:
                 raise KernelError("moe_linear: the two weight sets differ in shape")
         if x.shape[1] != K or out.shape[1] != N or offsets.numel() < n_experts + 1:
             raise KernelError("moe_linear: shapes do not agree")
+        n_places = out.shape[0]
+        if self.use_mma and self.use_tcgen05 and n_places >= MOE_TC_MIN_PLACES \
+                and out.dtype in (torch.bfloat16, torch.float32) and x.shape[1] % 8 == 0 \
+                and self.lib.nb_moe_gemm_tc_supported(dtype_code(x.dtype), dtype_code(w.dtype),
+                                                      n_places, n_experts, N, K):
+            # many rows (a prompt): tcgen05 tiles of 128 places; the rows are brought into the
+            # order of their places first, so that a tile is one TMA box
+            xs = x
+            if order is not None:
+                xs = torch.empty((n_places, K), device=x.device, dtype=x.dtype)
+                self._call("nb_moe_gather", _ptr(x), x.shape[1], _ptr(order), row_div, _ptr(offsets),
+                           n_experts, _ptr(xs), n_places, K, self._stream())
+            self._call("nb_moe_gemm_tc", _ptr(xs), xs.shape[0], _ptr(offsets), n_experts, n_places,
+                       _ptr(w), _ptr(w2), _ptr(out), dtype_code(out.dtype), out.shape[1], N, K, act,
+                       self._stream())
+            return
         if self.use_mma and out.dtype in (torch.bfloat16, torch.float32) \
                 and self.lib.nb_moe_gemm_mma_supported(dtype_code(x.dtype), dtype_code(w.dtype),
                                                        x.shape[1], K):

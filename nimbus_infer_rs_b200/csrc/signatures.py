@@ -61,6 +61,10 @@ SIGNATURES = {
     "nb_moe_gemm_mma": "pipipiipppiiiiip",
     "nb_head_linear_mma_supported": "iiiiii",
     "nb_head_linear_mma": "piiippipiipiiiip",
+    "nb_moe_gemm_tc_set_wait_budget": "l",
+    "nb_moe_gemm_tc_supported": "iiiiii",
+    "nb_moe_gather": "pipipipiip",
+    "nb_moe_gemm_tc": "pipiipppiiiiip",
     "nb_moe_route": "piipiiiippp",
     "nb_moe_group": "piipppp",
     "nb_moe_gemm_tiles": "ii",

@@ -277,7 +277,10 @@ def test_router_choice_order_ties_and_weights(ops):
 
 @pytest.mark.parametrize("dt,mma", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
 @pytest.mark.parametrize("rows,E,top,D,F", [(1, 1, 1, 8, 8), (3, 5, 2, 72, 24), (70, 4, 4, 64, 40),
-                                            (300, 8, 3, 128, 96), (9, 64, 6, 256, 72)])
+                                            (300, 8, 3, 128, 96), (9, 64, 6, 256, 72),
+                                            # many pairs: tcgen05 tiles (with tiles that reach
+                                            # into the next expert's rows and weight rows)
+                                            (700, 8, 3, 128, 96), (600, 3, 2, 320, 256), (1100, 40, 1, 64, 136)])
 def test_routed_experts_from_choice_to_sum(ops, dt, mma, rows, E, top, D, F):
     lay = build_layout([(1, [0] * rows, [])], [0], DEV, pad_rows_to=8)
     n = lay.n_rows
