@@ -407,12 +407,13 @@ def profile_ops(engine, peaks, batch, context, prefill):
     try:
         slots = [engine.alloc_slot() for _ in range(batch)]
         for i in range(0, batch, 16):
-            engine.step([(s, p, []) for s, p in zip(slots[i:i + 16], prompts_for(len(slots[i:i + 16]), context - 4, V, 5))])
-        for _ in range(2):
-            engine.step([(s, [1], [0]) for s in slots])
+            engine.step([(s, p, []) for s, p in zip(slots[i:i + 16], prompts_for(len(slots[i:i + 16]), context - 4, V, 5 + i))])
+        nxt = prompts_for(3, batch, V, 4)       # every sequence goes on with a token of its own
+        for k in range(2):
+            engine.step([(s, [tok], [0]) for s, tok in zip(slots, nxt[k])])
         timer.records = []
         torch.cuda.synchronize()
-        engine.step([(s, [1], [0]) for s in slots])
+        engine.step([(s, [tok], [0]) for s, tok in zip(slots, nxt[2])])
         out["decode"] = timer.table(peaks)
         for s in slots:
             engine.free_slot(s)
