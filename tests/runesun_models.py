@@ -26,6 +26,9 @@ def _layer(heads, dim, vdim, rank, scale, moe=None, weights_of=None):
 #    one; a single head; a layer run twice
 # Q: multiples of 8/16 (the tensor-core kernels' shapes), top = all experts in one layer
 # R: the smallest of everything
+# S: sizes that take the tensor-core kernels with ragged tiles (latents of 72, 8 and 200 in tiles
+#    of 96, 32 and 256; 7 heads; experts narrower than a tile), the first layer running with a
+#    later layer's tensors
 CONFIGS = {
     "P": {"architecture": "Runesun", "vocab": 257, "width": 72, "norm": {"eps": 3e-5}, "layers": [
         _layer(3, 20, 12, 40, 0.3, moe=(5, 2, 24)),
@@ -43,7 +46,13 @@ CONFIGS = {
         _layer(2, 3, 1, 2, 0.7, moe=(2, 1, 5)),
     ]},
 }
-SEEDS = {"P": 5, "Q": 6, "R": 7}
+CONFIGS["S"] = {"architecture": "Runesun", "vocab": 333, "width": 200, "norm": {"eps": 1e-5}, "layers": [
+    _layer(7, 24, 40, 72, 0.2, moe=(3, 3, 8), weights_of=2),
+    _layer(2, 8, 8, 8, 0.35, moe=(9, 4, 200)),
+    _layer(7, 24, 40, 72, 0.2, moe=(3, 3, 8)),
+    _layer(5, 16, 24, 200, 0.25),
+]}
+SEEDS = {"P": 5, "Q": 6, "R": 7, "S": 8}
 
 
 def make_tensors(cfg: dict, seed: int, sink_std: float = 1.5) -> dict[str, torch.Tensor]:

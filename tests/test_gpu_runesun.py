@@ -11,7 +11,7 @@ from gpu_helpers import DTYPES, TOL, assert_close
 from nimbus_infer_rs_b200 import Engine, SamplingParams
 
 pytestmark = pytest.mark.gpu
-NAMES = ["P", "Q", "R"]
+NAMES = ["P", "Q", "R", "S"]
 
 
 @pytest.fixture(scope="module")

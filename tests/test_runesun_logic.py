@@ -89,7 +89,7 @@ def test_missing_and_misshapen_tensors_are_listed(models, tmp_path):
     assert any("l3.mlp.e1.up" in w for w in e.value.wrong_shape)
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 def test_whole_prompts_and_token_by_token(models, cpu_backend, name):
     folder, cfg, P = models[name]
     e = Engine.load(folder, dtype="float32", device="cpu", cache_tokens=512)
