@@ -243,3 +243,52 @@ def test_the_comparison_sees_a_left_out_sink_gate_or_scale(models):
     P2 = dict(P, **{k.replace("l1.", "l2."): v for k, v in P.items() if k.startswith("l1.")})
     not_shared["layers"][2] = copy.deepcopy(cfg["layers"][1])
     assert moved(P2, not_shared) > 1e-2
+
+
+def test_trace_replay_as_a_program(models, tmp_path):
+    """bin/trace_run as a subprocess on a Runesun folder: three requests of unequal lengths in
+    one batch, decoded together while the shorter ones end, with exactly the tokens they hold as
+    --max-tokens; then the longest once more, whole, on what the batch gave back."""
+    import json
+    import subprocess
+    from pathlib import Path
+
+    import numpy as np
+    folder, cfg, P = models["S"]
+    root = Path(__file__).resolve().parent.parent
+    V = cfg["vocab"]
+    seqs = {"a": _tokens(V, 150, 1), "b": _tokens(V, 70, 2), "c": _tokens(V, 9, 3)}
+    heads = {"a": 140, "b": 66, "c": 1}
+    steps = [{"step": 0, "entries": [{"id": k, "tokens": seqs[k][:heads[k]], "want": [heads[k] - 1]}
+                                     for k in "abc"], "end": []}]
+    k = 0
+    while True:
+        live = [r for r in "abc" if heads[r] + k < len(seqs[r])]
+        if not live:
+            break
+        steps.append({"step": len(steps), "entries": [{"id": r, "tokens": [seqs[r][heads[r] + k]], "want": [0]}
+                                                      for r in live],
+                      "end": [r for r in live if heads[r] + k + 1 == len(seqs[r])]})
+        k += 1
+    steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": seqs["a"], "want": [0, 149]}],
+                  "end": ["a"]})
+    out = tmp_path / "out"
+    proc = subprocess.Popen([str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32",
+                             "--out", str(out), "--max-tokens", str(sum(len(v) for v in seqs.values()))],
+                            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, cwd="/")
+    for st in steps:
+        proc.stdin.write(json.dumps(st) + "\n")
+        proc.stdin.flush()
+        assert proc.stdout.readline().strip() == f"done {st['step']}"
+    proc.stdin.close()
+    assert proc.wait(timeout=120) == 0
+    refs = {r: PR.forward(seqs[r], P, cfg) for r in "abc"}
+    for st in steps[:-1]:
+        got = torch.from_numpy(np.fromfile(out / f"{st['step']}.f32", dtype="<f4").reshape(-1, V))
+        want = []
+        for e in st["entries"]:
+            at = heads[e["id"]] - 1 if st["step"] == 0 else heads[e["id"]] + st["step"] - 1
+            want.append(refs[e["id"]][at])
+        assert_close(got, torch.stack(want), "float32", f"step {st['step']}")
+    last = torch.from_numpy(np.fromfile(out / f"{len(steps) - 1}.f32", dtype="<f4").reshape(-1, V))
+    assert_close(last, refs["a"][[0, 149]], "float32", "the longest once more")
