@@ -89,6 +89,9 @@ class CacheGroup:
         self.max_pages = max(1, pages_for(max_seq_len))
         if request.planes not in (1, 2):
             raise ValueError(f"a cache request has 1 or 2 planes, not {request.planes}")
+        if request.every < 1 or (request.every > 1 and request.window):
+            raise ValueError(f"a cache request has an entry per token or per block of tokens "
+                             f"without a window, not {request}")
         self.storage = torch.zeros(
             (len(self.layers), request.planes, n_pages, request.n_kv_heads, PAGE, request.head_dim),
             dtype=dtype, device=device)
@@ -101,7 +104,9 @@ class CacheGroup:
         return self.storage.numel() * self.storage.element_size()
 
     def pages_needed(self, slot: int, n_tokens: int) -> int:
-        return max(0, pages_for(n_tokens) - len(self._pages.get(slot, ())))
+        """Pages the slot lacks to hold a sequence of ``n_tokens`` tokens: an entry per token,
+        or, in a store of pooled blocks, an entry per complete block of ``every`` tokens."""
+        return max(0, pages_for(n_tokens // self.request.every) - len(self._pages.get(slot, ())))
 
     def ensure(self, slot: int, n_tokens: int) -> None:
         need = self.pages_needed(slot, n_tokens)

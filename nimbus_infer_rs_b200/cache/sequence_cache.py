@@ -17,9 +17,11 @@ from .slots import CacheError, SlotAllocator
 class SequenceCache:
     def __init__(self, kv_requests: dict[int, KVRequest], state_requests: dict[int, StateRequest],
                  *, cache_tokens: int, max_seq_len: int, dtype: torch.dtype, device,
-                 n_slots: int | None = None):
+                 n_slots: int | None = None,
+                 extra_kv_requests: dict[tuple[int, int], KVRequest] | None = None):
         """``kv_requests`` / ``state_requests``: per schedule entry (a layer that runs twice
-        has two), for entries that keep storage of their own.  ``cache_tokens``: the most tokens live sequences hold at any time, each
+        has two), for entries that keep storage of their own.  ``extra_kv_requests``: the
+        further stores of an entry's mixer, by ``(entry, index)``.  ``cache_tokens``: the most tokens live sequences hold at any time, each
         sequence counted in whole pages of 64."""
         if cache_tokens <= 0:
             raise ValueError("cache_tokens must be positive")
@@ -32,9 +34,12 @@ class SequenceCache:
         self.device = device
         self.lens = [0] * self.n_slots
 
-        by_request: dict[KVRequest, list[int]] = {}
-        for layer, req in sorted(kv_requests.items()):
+        by_request: dict[KVRequest, list] = {}
+        self._n_extra: dict[int, int] = {}
+        for layer, req in sorted(kv_requests.items()) + sorted((extra_kv_requests or {}).items()):
             by_request.setdefault(req, []).append(layer)
+            if isinstance(layer, tuple):
+                self._n_extra[layer[0]] = max(self._n_extra.get(layer[0], 0), layer[1] + 1)
         self.groups = [CacheGroup(req, layers, self.n_pages, self.n_slots, self.max_seq_len,
                                   dtype, device) for req, layers in by_request.items()]
         self._group_of = {l: g for g in self.groups for l in g.layers}
@@ -47,6 +52,10 @@ class SequenceCache:
     def layer_kv(self, layer: int):
         g = self._group_of.get(layer)
         return None if g is None else g.layer_view(layer)
+
+    def layer_kv_extra(self, entry: int) -> tuple:
+        """The views of the further stores of a schedule entry's mixer, in the order asked."""
+        return tuple(self.layer_kv((entry, k)) for k in range(self._n_extra.get(entry, 0)))
 
     def layer_state(self, layer: int):
         return self.state.get(layer)

@@ -31,6 +31,9 @@ class Architecture:
     # Called with the raw config.json object; True if this architecture claims it when
     # no explicit name key is present.
     recognises: Callable[[dict], bool] | None = None
+    # (config, {tensor name: shape}) -> config: fills in sizes that config.json leaves to the
+    # weight file's tensor shapes; called before the model is built from a weight file
+    complete_config: Callable[[Any, dict], Any] | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}

@@ -207,6 +207,7 @@ moe_gemm_kernel(const TX* x, int x_stride, const int* order, int row_div, const 
       if (n >= N) continue;
       float v = acc[i][c];
       if (DUAL) v = nb_apply_act(v, act) * acc2[i][c];
+      else v = nb_apply_act(v, act);
       y[(size_t)p * y_stride + n] = nb_from_f32<TY>(v);
     }
   }

@@ -215,6 +215,7 @@ moe_mma_kernel(const TX* x, int x_stride, const int* order, int row_div, const i
           if (n >= N) continue;
           float v = acc[mi][nt][2 * half + c];
           if (DUAL) v = nb_apply_act_fast(v, act) * acc2[mi][nt][2 * half + c];
+          else v = nb_apply_act_fast(v, act);
           y[(size_t)p * y_stride + n] = nb_from_f32<TY>(scale == 0.0f ? 0.0f : v * scale);
         }
       }

@@ -158,6 +158,11 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             v[j] = __float_as_uint(nb_apply_act_fast(__uint_as_float(v[j]), act) * __uint_as_float(w[j]));
         }
         tc05_wait_ld();
+        if (!DUAL && act != NB_ACT_NONE) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = __float_as_uint(nb_apply_act_fast(__uint_as_float(v[j]), act));
+        }
         const int col0 = n0 + c * 32;
         if (p < end && col0 < N) {
           const bool whole = col0 + 32 <= N;

@@ -14,11 +14,13 @@ import os
 
 import torch
 
-ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU = 0, 1, 2, 3
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU, ACT_RELU2, ACT_TANH, ACT_XIELU = 0, 1, 2, 3, 4, 5, 6
 # what a dense product's epilogue can apply
 ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GELU_ERF}
-# what the gate of a gated feed-forward (routed experts) can be
-GATE_ACTIVATIONS = {**ACTIVATIONS, "silu": ACT_SILU}
+# what the experts' first product (routed experts) can apply
+GATE_ACTIVATIONS = {**ACTIVATIONS, "silu": ACT_SILU, "relu2": ACT_RELU2}
+# what a pass over fp32 rows can apply (`act_rows`): those, and activations with learned numbers
+ROW_ACTIVATIONS = {"tanh": ACT_TANH, "xielu": ACT_XIELU}
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 DECODE_TARGET_CTAS = 4 * 148   # CTAs the split 32-bit decode attention aims to put on the GPU
@@ -167,7 +169,7 @@ class CudaBackend:
             raise KernelError(f"{fn_name} failed ({rc}): {msg}")
 
     # -- row-wise ---------------------------------------------------------------------
-    def embed_pos(self, tokens, pos, wte, wpe, out):
+    def embed_pos(self, tokens, pos, wte, wpe, out, scale=1.0):
         _check(tokens, "tokens", torch.int32, 1)
         _check(pos, "pos", torch.int32, 1)
         _check(wte, "wte", None, 2)
@@ -178,7 +180,7 @@ class CudaBackend:
         if tokens.numel() < n or pos.numel() < n or wte.shape[1] != d:
             raise KernelError("embed_pos: shapes do not agree")
         self._call("nb_embed_pos", _ptr(tokens), _ptr(pos), _ptr(wte), _ptr(wpe),
-                   dtype_code(wte.dtype), _ptr(out), n, d, self._stream())
+                   dtype_code(wte.dtype), _ptr(out), n, d, float(scale), self._stream())
 
     def layernorm(self, x, gamma, beta, eps, out, rows=None):
         _check(x, "x", torch.float32, 2)
@@ -209,6 +211,56 @@ class CudaBackend:
             raise KernelError("rmsnorm: shapes do not agree")
         self._call("nb_rmsnorm", _ptr(x), x.shape[1], x_col, _ptr(rows), _ptr(gamma), _ptr(out),
                    dtype_code(out.dtype), n, d, eps, self._stream())
+
+    def rms_add(self, y, gamma, eps, residual, next_gamma, next_eps, out_next, out_cast):
+        """``residual += y / sqrt(mean(y^2) + eps) * gamma`` per row (fp32), and in the same pass,
+        where asked for, ``out_next = rms-norm(residual) * next_gamma`` and ``out_cast =
+        residual`` in the activation type."""
+        _check(y, "y", torch.float32, 2)
+        _check(residual, "residual", torch.float32, 2)
+        _check(gamma, "gamma", torch.float32, 1)
+        n, d = residual.shape
+        if y.shape != residual.shape or gamma.numel() != d:
+            raise KernelError("rms_add: shapes do not agree")
+        code = 0
+        for t, nm in ((out_next, "out_next"), (out_cast, "out_cast")):
+            if t is not None:
+                _check(t, nm, None, 2)
+                if t.shape != residual.shape:
+                    raise KernelError(f"rms_add: {nm} shape does not match")
+                code = dtype_code(t.dtype)
+        if out_next is not None and out_cast is not None and out_next.dtype != out_cast.dtype:
+            raise KernelError("rms_add: the two outputs differ in type")
+        if out_next is not None:
+            _check(next_gamma, "next_gamma", torch.float32, 1)
+        self._call("nb_rms_add", _ptr(y), _ptr(gamma), float(eps), _ptr(residual),
+                   _ptr(next_gamma if out_next is not None else None), float(next_eps),
+                   _ptr(out_next), _ptr(out_cast), code, n, d, self._stream())
+
+    def act_rows(self, x, x_col, act, params, out):
+        """``out[r, i] = act(x[r, x_col + i])`` for fp32 rows ``x``: ``ACT_TANH``, or ``ACT_XIELU``
+        with its two learned numbers in ``params`` (fp32 ``[2]``), or an epilogue activation."""
+        _check(x, "x", torch.float32, 2)
+        _check(out, "out", None, 2)
+        if params is not None:
+            _check(params, "params", torch.float32, 1)
+        n, d = out.shape
+        if x.shape[0] < n or x.shape[1] < x_col + d:
+            raise KernelError("act_rows: shapes do not agree")
+        self._call("nb_act_rows", _ptr(x), x.shape[1], x_col, int(act), _ptr(params), _ptr(out),
+                   dtype_code(out.dtype), n, d, self._stream())
+
+    def gather_mul(self, g, table, tokens, out):
+        """``out[r] = g[r] * table[tokens[r]]`` (fp32 gate ``g``; zeros for padding rows)."""
+        _check(g, "g", torch.float32, 2)
+        _check(table, "table", None, 2)
+        _check(tokens, "tokens", torch.int32, 1)
+        _check(out, "out", None, 2)
+        n, d = out.shape
+        if g.shape != out.shape or table.shape[1] != d or tokens.numel() < n:
+            raise KernelError("gather_mul: shapes do not agree")
+        self._call("nb_gather_mul", _ptr(g), _ptr(table), dtype_code(table.dtype), _ptr(tokens),
+                   _ptr(out), dtype_code(out.dtype), n, d, self._stream())
 
     # -- matrix products --------------------------------------------------------------
     def linear(self, x, w, bias, out, act=ACT_NONE, residual=None, norm=None):
@@ -568,6 +620,78 @@ class CudaBackend:
                    _ptr(kv.block_table), kv.block_table.shape[1], kv.page, n_heads, rank,
                    _ptr(sink), _ptr(out), dtype_code(out.dtype), out.shape[1], scale, window, n,
                    self._stream())
+
+    # -- windowed attention with pooled blocks; the delta rule --------------------------
+    def qk_norm_rope_append(self, src, q_col, k_col, q_gamma, k_gamma, eps, freq, rot_dims,
+                            amplitude, layout, kv, n_heads, q_out, write):
+        """Per head: RMS norm (weights ``q_gamma`` / ``k_gamma`` over the head) and rotation by
+        position of the queries and keys in the fp32 rows ``src``; queries to ``q_out``, keys to
+        the K plane of ``kv`` and the keys as projected to its V plane (``write``)."""
+        _check(src, "src", torch.float32, 2)
+        _check(q_out, "q_out", None, 2)
+        d, G = kv.head_dim, kv.n_kv_heads
+        n = layout.n_rows
+        if q_out.shape != (n, n_heads * d) or src.shape[0] < n or \
+                src.shape[1] < max(q_col + n_heads * d, k_col + G * d) or \
+                q_gamma.numel() != d or k_gamma.numel() != d or \
+                (rot_dims and (freq is None or freq.numel() != rot_dims // 2)):
+            raise KernelError("qk_norm_rope_append: shapes do not agree")
+        self._call("nb_qk_norm_rope_append", _ptr(src), src.shape[1], q_col, k_col, _ptr(q_gamma),
+                   _ptr(k_gamma), float(eps), _ptr(freq), int(rot_dims), float(amplitude),
+                   _ptr(layout.row_slot), _ptr(layout.row_pos), _ptr(q_out), dtype_code(q_out.dtype),
+                   _ptr(kv.k), _ptr(kv.v), dtype_code(kv.k.dtype), _ptr(kv.block_table),
+                   kv.block_table.shape[1], kv.page, n_heads, G, d, 1 if write else 0, n,
+                   self._stream())
+
+    def pool_blocks(self, layout, kv, blocks, pool):
+        """For every row that completes a block of ``pool`` tokens: the means of the block's keys
+        and values in ``kv`` into entry ``pos // pool`` of the paged store ``blocks``."""
+        if blocks.k.dtype != kv.k.dtype or blocks.head_dim != kv.head_dim or \
+                blocks.n_kv_heads != kv.n_kv_heads or blocks.page != kv.page:
+            raise KernelError("pool_blocks: the two stores differ in shape or type")
+        self._call("nb_pool_blocks", _ptr(layout.row_slot), _ptr(layout.row_pos), _ptr(kv.k),
+                   _ptr(kv.v), _ptr(kv.block_table), kv.block_table.shape[1], _ptr(blocks.k),
+                   _ptr(blocks.v), _ptr(blocks.block_table), blocks.block_table.shape[1],
+                   dtype_code(kv.k.dtype), kv.page, kv.n_kv_heads, kv.head_dim, int(pool),
+                   layout.n_rows, self._stream())
+
+    def attention_pooled(self, q, layout, kv, blocks, n_heads, sink, out, scale, window, pool):
+        """Attention of the packed rows over the last ``window`` tokens of ``kv`` and the pooled
+        blocks (``blocks``, or ``None``) that lie wholly before the window, with a sink."""
+        _check(q, "q", None, 2)
+        _check(out, "out", None, 2)
+        n, d = layout.n_rows, kv.head_dim
+        if q.shape != (n, n_heads * d) or out.shape != (n, n_heads * d):
+            raise KernelError("attention_pooled: shapes do not agree")
+        if sink is not None:
+            _check(sink, "sink", torch.float32, 1)
+        self._call("nb_attention_pooled", _ptr(q), dtype_code(q.dtype), _ptr(layout.row_slot),
+                   _ptr(layout.row_pos), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table),
+                   kv.block_table.shape[1], _ptr(blocks.k if blocks is not None else None),
+                   _ptr(blocks.v if blocks is not None else None),
+                   _ptr(blocks.block_table if blocks is not None else None),
+                   blocks.block_table.shape[1] if blocks is not None else 0,
+                   dtype_code(kv.k.dtype), kv.page, n_heads, kv.n_kv_heads, d, _ptr(sink), _ptr(out),
+                   dtype_code(out.dtype), float(scale), int(window), int(pool), n, self._stream())
+
+    def delta_rule(self, fused, col_r, col_k, col_v, col_g, col_a, decay_logits, a_bias, norm_w,
+                   eps, decay_rate, key_eps, layout, state, n_heads, dim, out):
+        """The generalized delta rule over each sequence's rows in order, from and into the
+        sequences' state rows (``state``: fp32 ``[n_slots, n_heads * dim * dim]``); the heads'
+        outputs normed, weighted and gated into ``out``."""
+        _check(fused, "fused", torch.float32, 2)
+        _check(decay_logits, "decay_logits", torch.float32, 2)
+        _check(state, "state", torch.float32, 2)
+        _check(out, "out", None, 2)
+        n, hd = layout.n_rows, n_heads * dim
+        if out.shape != (n, hd) or decay_logits.shape != (n, hd) or a_bias.numel() != hd or \
+                norm_w.numel() != hd or state.shape[1] != hd * dim or \
+                fused.shape[1] < max(col_r, col_k, col_v, col_g, col_a) + hd:
+            raise KernelError("delta_rule: shapes do not agree")
+        self._call("nb_delta_rule", _ptr(fused), fused.shape[1], col_r, col_k, col_v, col_g, col_a,
+                   _ptr(decay_logits), _ptr(a_bias), _ptr(norm_w), float(eps), float(decay_rate),
+                   float(key_eps), _ptr(layout.cu_rows), _ptr(layout.seq_slot), _ptr(state), _ptr(out),
+                   dtype_code(out.dtype), n_heads, dim, layout.n_seqs, n, self._stream())
 
     # -- routed experts ---------------------------------------------------------------
     def moe_route(self, logits, col, n_experts, top, renormalize, layout, idx, weight):

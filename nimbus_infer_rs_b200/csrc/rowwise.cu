@@ -61,13 +61,13 @@ NB_EXPORT void nb_set_overlap(int on) { g_overlap = on; }
 NB_EXPORT int nb_get_overlap() { return g_overlap; }
 
 // ---------------------------------------------------------------------------------
-// x[r] = wte[token[r]] + wpe[pos[r]]   (src/model.rs:285-295), fp32 result.
+// x[r] = scale * wte[token[r]] + wpe[pos[r]]   (src/model.rs:285-295, scale 1), fp32 result.
 // A negative token marks a padding row: it is written as zeros.
 // ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_pos_kernel(const int* tokens, const int* pos,
                                  const T* __restrict__ wte, const T* __restrict__ wpe,
-                                 float* out, int d) {
+                                 float* out, int d, float scale) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
   const int r = blockIdx.x;
@@ -80,23 +80,25 @@ __global__ void embed_pos_kernel(const int* tokens, const int* pos,
   const T* e = wte + (size_t)tok * d;
   if (wpe != nullptr) {
     const T* p = wpe + (size_t)pos[r] * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = nb_to_f32(e[i]) + nb_to_f32(p[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = nb_to_f32(e[i]) * scale + nb_to_f32(p[i]);
   } else {
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = nb_to_f32(e[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = nb_to_f32(e[i]) * scale;
   }
 }
 
 NB_EXPORT int nb_embed_pos(const int* tokens, const int* pos, const void* wte, const void* wpe,
-                           int table_dtype, float* out, int n_rows, int d, cudaStream_t stream) {
+                           int table_dtype, float* out, int n_rows, int d, float scale,
+                           cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NB_REQUIRE(n_rows > 0 && d > 0, NB_ERR_BAD_ARG, "embed_pos: bad sizes rows=%d d=%d", n_rows, d);
   const int threads = d >= 256 ? 256 : (d >= 128 ? 128 : 64);
   if (table_dtype == NB_F32)
     NB_CUDA(nb_launch(embed_pos_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, tokens, pos,
-                      (const float*)wte, (const float*)wpe, out, d));
+                      (const float*)wte, (const float*)wpe, out, d, scale));
   else if (table_dtype == NB_BF16)
     NB_CUDA(nb_launch(embed_pos_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream,
-                      tokens, pos, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, d));
+                      tokens, pos, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, d,
+                      scale));
   else
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "embed_pos: unknown table dtype %d", table_dtype);
   NB_CHECK_LAUNCH("embed_pos");
@@ -333,6 +335,177 @@ NB_EXPORT int nb_rmsnorm(const float* x, int x_stride, int x_col, const int* row
   else
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "rmsnorm: unknown output dtype %d", out_dtype);
   NB_CHECK_LAUNCH("rmsnorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// A sublayer's normed result added to the stream, and what the stream's next reader wants, in
+// one pass over a row:  x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * gamma            (fp32)
+//   out_next[r] = x[r] / sqrt(mean(x[r]^2) + next_eps) * next_gamma   if out_next  (TOut)
+//   out_cast[r] = x[r]                                                if out_cast  (TOut)
+// The row stays in registers between the two norms (width <= RA_MAX * threads).
+// ---------------------------------------------------------------------------------
+constexpr int RA_MAX = 8;
+
+template <typename TOut>
+__global__ void rms_add_kernel(const float* y, const float* __restrict__ gamma, float eps, float* x,
+                               const float* __restrict__ next_gamma, float next_eps,
+                               TOut* out_next, TOut* out_cast, int d) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const float* yr = y + (size_t)r * d;
+  float* xr = x + (size_t)r * d;
+  float v[RA_MAX];
+  float ss = 0.0f;
+#pragma unroll
+  for (int a = 0; a < RA_MAX; ++a) {
+    const int i = threadIdx.x + a * blockDim.x;
+    v[a] = i < d ? yr[i] : 0.0f;
+    ss = fmaf(v[a], v[a], ss);
+  }
+  ss = nb_block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+  float s2 = 0.0f;
+#pragma unroll
+  for (int a = 0; a < RA_MAX; ++a) {
+    const int i = threadIdx.x + a * blockDim.x;
+    if (i < d) {
+      v[a] = xr[i] + v[a] * inv * gamma[i];
+      xr[i] = v[a];
+      if (out_cast != nullptr) out_cast[(size_t)r * d + i] = nb_from_f32<TOut>(v[a]);
+    } else {
+      v[a] = 0.0f;
+    }
+    s2 = fmaf(v[a], v[a], s2);
+  }
+  if (out_next == nullptr) return;
+  s2 = nb_block_sum(s2, red);
+  const float inv2 = 1.0f / sqrtf(s2 / (float)d + next_eps);
+#pragma unroll
+  for (int a = 0; a < RA_MAX; ++a) {
+    const int i = threadIdx.x + a * blockDim.x;
+    if (i < d) out_next[(size_t)r * d + i] = nb_from_f32<TOut>(v[a] * inv2 * next_gamma[i]);
+  }
+}
+
+NB_EXPORT int nb_rms_add(const float* y, const float* gamma, float eps, float* x,
+                         const float* next_gamma, float next_eps, void* out_next, void* out_cast,
+                         int out_dtype, int n_rows, int d, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0 && d <= RA_MAX * 1024, NB_ERR_BAD_ARG,
+             "rms_add: bad sizes rows=%d d=%d", n_rows, d);
+  NB_REQUIRE(gamma != nullptr && (out_next == nullptr || next_gamma != nullptr), NB_ERR_BAD_ARG,
+             "rms_add: a norm without its weight");
+  int threads = 64;
+  while (threads < 1024 && threads * (d > 2048 ? RA_MAX : 4) < d) threads *= 2;
+  if (out_dtype == NB_F32)
+    NB_CUDA(nb_launch(rms_add_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, y, gamma, eps,
+                      x, next_gamma, next_eps, (float*)out_next, (float*)out_cast, d));
+  else if (out_dtype == NB_BF16)
+    NB_CUDA(nb_launch(rms_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, y,
+                      gamma, eps, x, next_gamma, next_eps, (__nv_bfloat16*)out_next,
+                      (__nv_bfloat16*)out_cast, d));
+  else
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "rms_add: unknown output dtype %d", out_dtype);
+  NB_CHECK_LAUNCH("rms_add");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// out[r, i] = act(x[r, x_col + i]) for fp32 rows x: activations that a product's epilogue does
+// not carry.  NB_ACT_TANH; NB_ACT_XIELU with two learned numbers p, q read from `params`:
+//   z > 0:  softplus(p) z^2 + z/2;   z <= 0:  (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ float nb_softplus(float x) {
+  return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x)));
+}
+
+template <typename TOut>
+__global__ void act_rows_kernel(const float* x, int x_stride, int x_col, int act,
+                                const float* __restrict__ params, TOut* out, int d, size_t total) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  float ap = 0.0f, an = 0.0f;
+  if (act == NB_ACT_XIELU) {
+    ap = nb_softplus(params[0]);
+    an = 0.5f + nb_softplus(params[1]);
+  }
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = e / d;
+    const int i = (int)(e - r * d);
+    const float z = x[r * x_stride + x_col + i];
+    float v;
+    if (act == NB_ACT_XIELU)
+      v = z > 0.0f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+    else if (act == NB_ACT_TANH)
+      v = tanhf(z);
+    else
+      v = nb_apply_act(z, act);
+    out[e] = nb_from_f32<TOut>(v);
+  }
+}
+
+NB_EXPORT int nb_act_rows(const float* x, int x_stride, int x_col, int act, const float* params,
+                          void* out, int out_dtype, int n_rows, int d, cudaStream_t stream) {
+  if (n_rows == 0 || d == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0 && x_col >= 0 && x_stride >= x_col + d, NB_ERR_BAD_ARG,
+             "act_rows: bad sizes rows=%d d=%d col=%d stride=%d", n_rows, d, x_col, x_stride);
+  NB_REQUIRE(act != NB_ACT_XIELU || params != nullptr, NB_ERR_BAD_ARG,
+             "act_rows: this activation has learned numbers");
+  const size_t total = (size_t)n_rows * d;
+  const int blocks = (int)((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
+  if (out_dtype == NB_F32)
+    NB_CUDA(nb_launch(act_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, x_stride,
+                      x_col, act, params, (float*)out, d, total));
+  else if (out_dtype == NB_BF16)
+    NB_CUDA(nb_launch(act_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x,
+                      x_stride, x_col, act, params, (__nv_bfloat16*)out, d, total));
+  else
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "act_rows: unknown output dtype %d", out_dtype);
+  NB_CHECK_LAUNCH("act_rows");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// out[r, i] = g[r, i] * table[token[r], i]: a gate times the token's row of a table (fp32 gate,
+// product in fp32).  Padding rows (token < 0) give zeros.
+// ---------------------------------------------------------------------------------
+template <typename TT, typename TOut>
+__global__ void gather_mul_kernel(const float* g, const TT* __restrict__ table, const int* tokens,
+                                  TOut* out, int d, size_t total) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = e / d;
+    const int i = (int)(e - r * d);
+    const int tok = tokens[r];
+    out[e] = nb_from_f32<TOut>(tok < 0 ? 0.0f : g[e] * nb_to_f32(table[(size_t)tok * d + i]));
+  }
+}
+
+NB_EXPORT int nb_gather_mul(const float* g, const void* table, int table_dtype, const int* tokens,
+                            void* out, int out_dtype, int n_rows, int d, cudaStream_t stream) {
+  if (n_rows == 0 || d == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0, NB_ERR_BAD_ARG, "gather_mul: bad sizes rows=%d d=%d", n_rows, d);
+  const size_t total = (size_t)n_rows * d;
+  const int blocks = (int)((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
+  typedef __nv_bfloat16 bf;
+#define NB_GM(TT, TO)                                                                          \
+  NB_CUDA(nb_launch(gather_mul_kernel<TT, TO>, dim3(blocks), dim3(256), 0, stream, g,          \
+                    (const TT*)table, tokens, (TO*)out, d, total))
+  switch (table_dtype * 2 + out_dtype) {
+    case 0: NB_GM(float, float); break;
+    case 1: NB_GM(float, bf); break;
+    case 2: NB_GM(bf, float); break;
+    case 3: NB_GM(bf, bf); break;
+    default: NB_REQUIRE(false, NB_ERR_BAD_ARG, "gather_mul: unknown dtypes %d/%d", table_dtype, out_dtype);
+  }
+#undef NB_GM
+  NB_CHECK_LAUNCH("gather_mul");
   return 0;
 }
 

@@ -49,7 +49,15 @@ SIGNATURES = {
     "nb_abi_version": "",
     "nb_set_overlap": "i",
     "nb_get_overlap": "",
-    "nb_embed_pos": "ppppipiip",
+    "nb_embed_pos": "ppppipiifp",
+    "nb_rms_add": "ppfppfppiiip",
+    "nb_act_rows": "piiippiiip",
+    "nb_gather_mul": "ppippiiip",
+    "nb_qk_norm_rope_append": "piiippfpifpppippipiiiiiiip",
+    "nb_pool_blocks": "pppppipppiiiiiiip",
+    "nb_attention_pooled": "pipppppipppiiiiiippifiiip",
+    "nb_delta_rule_supported": "i",
+    "nb_delta_rule": "piiiiiipppfffppppiiiiip",
     "nb_layernorm": "pppppiiifp",
     "nb_rmsnorm": "piipppiiifp",
     "nb_latent_append": "piipfpppipiiiip",

@@ -18,6 +18,7 @@ class StepContext:
     # storage of the schedule entry that is running (set by the model before each layer)
     kv: Any = None           # LayerKV or None
     state: Any = None        # fp32 [n_slots, n_elements] or None
+    kv_extra: Any = ()       # LayerKV of the mixer's further stores, in the order it asked
     writes_cache: bool = True
     # what a layer's mixer leaves for the feed-forward beside it: (fp32 rows, first column)
     shared_projection: Any = None

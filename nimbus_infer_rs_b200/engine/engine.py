@@ -50,7 +50,8 @@ class Engine:
             model.kv_source(entry)          # a bad cache_from fails here, not in a step
         self.cache = SequenceCache(kv_req, st_req, cache_tokens=cache_tokens,
                                    max_seq_len=self.spec.max_seq_len, dtype=self.rt.act_dtype,
-                                   device=self.rt.device, n_slots=n_slots)
+                                   device=self.rt.device, n_slots=n_slots,
+                                   extra_kv_requests=model.extra_storage_requests())
         # steps of a shape that comes again are replayed as CUDA graphs (``step_graphs = None``
         # keeps every step on plain launches)
         self.step_graphs = StepGraphs(self) if (
@@ -71,9 +72,12 @@ class Engine:
             raise ValueError(f"dtype must be one of {sorted(PRECISIONS)}, got {dtype!r}")
         arch, config = load_config(model_dir)
         rt = Runtime(torch.device(device), PRECISIONS[dtype])
-        spec = arch.build_spec(config)
-        model = Model(spec, rt)
         with SafeTensorsFile(find_weight_file(model_dir)) as f:
+            if arch.complete_config is not None:
+                # sizes that only the tensors' shapes give
+                config = arch.complete_config(config, {n: tuple(f.info(n).shape) for n in f.names()})
+            spec = arch.build_spec(config)
+            model = Model(spec, rt)
             plan = arch.weight_plan(config, spec, set(f.names()))
             params = load_params(model.param_specs(), plan, f, precision=rt.precision,
                                  device=rt.device, cast_weights=cast_weights)

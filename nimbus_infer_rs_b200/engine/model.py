@@ -40,11 +40,18 @@ class Layer:
         self.mixer = build_part("mixer", spec.mixer)
         self.norm_ffn = build_part("norm", spec.norm_ffn) if spec.norm_ffn is not None else None
         self.ffn = build_part("ffn", spec.ffn) if spec.ffn is not None else None
+        self.post_norm_mixer = build_part("norm", spec.post_norm_mixer) \
+            if spec.post_norm_mixer is not None else None
+        self.post_norm_ffn = build_part("norm", spec.post_norm_ffn) \
+            if spec.post_norm_ffn is not None else None
+        self.side = build_part("side", spec.side) if spec.side is not None else None
 
     def parts(self):
         """The layer's parts that exist, by the name their parameters are listed under."""
         named = {"norm_mixer": self.norm_mixer, "mixer": self.mixer,
-                 "norm_ffn": self.norm_ffn, "ffn": self.ffn}
+                 "norm_ffn": self.norm_ffn, "ffn": self.ffn,
+                 "post_norm_mixer": self.post_norm_mixer, "post_norm_ffn": self.post_norm_ffn,
+                 "side": self.side}
         return {k: v for k, v in named.items() if v is not None}
 
 
@@ -53,7 +60,7 @@ class Model:
         spec.validate()
         self.spec = spec
         self.rt = runtime
-        self.embedding = TokenEmbedding(spec.vocab_size, spec.width)
+        self.embedding = TokenEmbedding(spec.vocab_size, spec.width, spec.embedding_scale)
         self.position = build_part("position", spec.position)
         self.layers = [Layer(i, ls) for i, ls in enumerate(spec.layers)]
         self.final_norm = build_part("norm", spec.final_norm)
@@ -114,6 +121,7 @@ class Model:
         for entry, li in enumerate(self.run_order):
             layer = self.layers[li]
             ctx.kv, ctx.state, ctx.writes_cache = self.storage_of(ctx.cache, entry)
+            ctx.kv_extra = ctx.cache.layer_kv_extra(entry)
             layer.block.forward(ctx, x, layer)
         return x
 
@@ -142,6 +150,14 @@ class Model:
             if s is not None:
                 st[entry] = s
         return kv, st
+
+    def extra_storage_requests(self):
+        """The further paged stores of each schedule entry's mixer: ``{(entry, k): KVRequest}``."""
+        out = {}
+        for entry, li in enumerate(self.run_order):
+            for k, r in enumerate(self.layers[li].mixer.extra_cache_requests()):
+                out[(entry, k)] = r
+        return out
 
     def kv_source(self, entry: int) -> int:
         """The schedule entry whose key/value store ``entry`` uses: itself, or the latest

@@ -24,6 +24,11 @@ class LayerSpec:
     norm_ffn: PartSpec | None
     block: PartSpec = PartSpec("pre_norm")
     cache_from: int | None = None
+    # norms of the sublayers' results, for an arrangement that has them (``sandwich``)
+    post_norm_mixer: PartSpec | None = None
+    post_norm_ffn: PartSpec | None = None
+    # a per-token input added to the stream after the sublayers
+    side: PartSpec | None = None
 
 
 @dataclass(frozen=True)
@@ -37,6 +42,7 @@ class ModelSpec:
     final_norm: PartSpec
     tie_head: bool = True
     schedule: tuple[int, ...] | None = None
+    embedding_scale: float = 1.0      # multiplies the token embedding (not the tied head)
 
     def run_order(self) -> tuple[int, ...]:
         order = self.schedule if self.schedule is not None else tuple(range(len(self.layers)))

@@ -1,5 +1,5 @@
 from .base import (INDEX, MATRIX, TABLE, VECTOR, Block, DeferredNorm, FeedForward, KVRequest, Mixer, Norm,
-                   ParamSpec, Part, PartSpec, Position, StateRequest, bind_params, build_part,
+                   ParamSpec, Part, PartSpec, Position, Side, StateRequest, bind_params, build_part,
                    collect_param_specs, register_part, registered_parts)
 from .linear import Linear
 from .norm import LayerNorm, RMSNorm
@@ -10,3 +10,7 @@ from .latent_attention import LatentAttention
 from .feed_forward import DenseMLP
 from .routed_experts import RoutedExperts
 from .block import ParallelBlock, PreNormBlock
+from .pooled_attention import PooledWindowAttention
+from .delta_rule import DeltaRule
+from .token_side import GatedTokenInput
+from .block import SandwichBlock

@@ -1,7 +1,7 @@
 """Interfaces of the parts a model is assembled from, and their registries.
 
 A *part* is built from a :class:`PartSpec` (a kind name plus keyword arguments: all of
-its sizes and constants) and knows nothing about the model it sits in.  There are five
+its sizes and constants) and knows nothing about the model it sits in.  There are six
 families, each with its own registry:
 
 =============  ===========================================================================
@@ -19,6 +19,8 @@ family         interface
 ``block``      ``forward(ctx, x, layer)``: the arrangement of norms, mixer and feed-forward
                around the residual stream of one layer (``layer.ffn`` and ``layer.norm_ffn``
                are ``None`` in a layer without them)
+``side``       ``forward(ctx, x, x_act)``: a per-token input that a layer adds to the stream
+               after its sublayers (``x_act``: the stream's rows in the activation type)
 =============  ===========================================================================
 
 Every part lists its parameters with :meth:`Part.param_specs` (shape and role) and gets the
@@ -59,11 +61,14 @@ class KVRequest:
     """Growing per-sequence storage a mixer needs: keys and values for every cached token.
     ``window`` > 0 means only the last ``window`` tokens are ever read.  ``planes``: 2 for keys
     and values, 1 for a mixer that keeps one vector per token and head (a latent that is key
-    and value at once)."""
+    and value at once).  ``every`` > 1: one entry per ``every`` tokens of the sequence instead of
+    one per token (a store of pooled blocks: entry ``b`` belongs to tokens ``b * every ..
+    b * every + every - 1`` and exists once the last of them is cached)."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     planes: int = 2
+    every: int = 1
 
 
 @dataclass(frozen=True)
@@ -149,11 +154,20 @@ class Mixer(Part):
     def state_request(self) -> StateRequest | None:
         return None
 
+    def extra_cache_requests(self) -> tuple[KVRequest, ...]:
+        """Further paged stores beside the one of :meth:`cache_request` (pooled blocks, say);
+        the running entry's views of them are ``ctx.kv_extra``, in this order."""
+        return ()
+
     def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor) -> None:
         """``ctx.kv``: the paged key/value store of this schedule entry (or of the entry it
         reads from, then ``ctx.writes_cache`` is False); ``ctx.state``: fp32 tensor
         [n_slots, n_elements] or None.  Storage belongs to the schedule entry, not to the
-        layer: a layer that runs twice keeps two caches."""
+        layer: a layer that runs twice keeps two caches.
+
+        A part that sets ``can_overwrite = True`` also takes ``accumulate=False``: it then
+        writes its result over ``residual`` instead of adding to it (an arrangement that norms
+        a sublayer's result before the addition hands it a buffer of its own)."""
         raise NotImplementedError
 
 
@@ -165,6 +179,13 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Side(Part):
+    family = "side"
+
+    def forward(self, ctx, x: torch.Tensor, x_act: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
 class Block(Part):
     family = "block"
 
@@ -173,7 +194,7 @@ class Block(Part):
 
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Part]]] = {
-    "norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {},
+    "norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {}, "side": {},
 }
 
 

@@ -1,6 +1,8 @@
 """Arrangements of norms, mixer and feed-forward around the residual stream."""
 from __future__ import annotations
 
+import torch
+
 from .base import Block, register_part
 
 
@@ -38,3 +40,44 @@ class ParallelBlock(Block):
         layer.mixer.forward(ctx, h, x)
         if layer.ffn is not None:
             layer.ffn.forward(ctx, h, x)
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Block):
+    """A norm before and after each sublayer: ``x += post_norm_mixer(mixer(norm_mixer(x)))``,
+    then ``x += post_norm_ffn(ffn(norm_ffn(x)))`` (the feed-forward may be absent), then the
+    layer's per-token input if it has one (``layer.side``), which reads the stream itself.
+
+    A sublayer writes its result into an fp32 buffer of its own (a part that cannot overwrite
+    gets zeros to add to); one pass over the rows norms that result, adds it to the stream and
+    produces what the next reader wants: the next sublayer's normed rows, or the stream rounded
+    to the activation type for the per-token input."""
+    graph_safe = True
+
+    def __init__(self):
+        pass
+
+    @staticmethod
+    def _run(part, ctx, h, like):
+        if getattr(part, "can_overwrite", False):
+            y = torch.empty_like(like)
+            part.forward(ctx, h, y, accumulate=False)
+        else:
+            y = torch.zeros_like(like)
+            part.forward(ctx, h, y)
+        return y
+
+    def forward(self, ctx, x, layer) -> None:
+        side = layer.side
+        # the side input multiplies the stream by a matrix: in a 32-bit run the stream itself
+        wants_rounded = side is not None and ctx.rt.act_dtype != torch.float32
+        h = layer.norm_mixer.forward(ctx, x)
+        y = self._run(layer.mixer, ctx, h, x)
+        if layer.ffn is not None:
+            h, _ = layer.post_norm_mixer.add_into(ctx, y, x, then=layer.norm_ffn)
+            y = self._run(layer.ffn, ctx, h, x)
+            _, xr = layer.post_norm_ffn.add_into(ctx, y, x, rounded=wants_rounded)
+        else:
+            _, xr = layer.post_norm_mixer.add_into(ctx, y, x, rounded=wants_rounded)
+        if side is not None:
+            side.forward(ctx, x, xr if wants_rounded else x)

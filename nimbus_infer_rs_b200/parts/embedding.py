@@ -7,15 +7,16 @@ from .base import MATRIX, TABLE, DeferredNorm, ParamSpec, Part
 
 
 class TokenEmbedding(Part):
-    """``x[i] = table[token_i] (+ position_table[pos_i])`` into the fp32 residual stream
-    (src/model.rs:285-295)."""
+    """``x[i] = scale * table[token_i] (+ position_table[pos_i])`` into the fp32 residual stream
+    (src/model.rs:285-295; ``scale`` is 1 there)."""
     graph_safe = True
     family = "embedding"
     kind = "token_embedding"
 
-    def __init__(self, vocab_size: int, width: int):
+    def __init__(self, vocab_size: int, width: int, scale: float = 1.0):
         self.vocab_size = int(vocab_size)
         self.width = int(width)
+        self.scale = float(scale)
         self.table = None
 
     def param_specs(self):
@@ -24,7 +25,7 @@ class TokenEmbedding(Part):
     def forward(self, ctx, position) -> torch.Tensor:
         lay = ctx.layout
         x = torch.empty((lay.n_rows, self.width), device=self.table.device, dtype=torch.float32)
-        ctx.ops.embed_pos(lay.tokens, lay.row_pos, self.table, position.table, x)
+        ctx.ops.embed_pos(lay.tokens, lay.row_pos, self.table, position.table, x, self.scale)
         return x
 
 

@@ -3,8 +3,8 @@ from __future__ import annotations
 
 import torch
 
-from ..csrc.ops import ACTIVATIONS
-from .base import FeedForward, register_part
+from ..csrc.ops import ACTIVATIONS, ROW_ACTIVATIONS
+from .base import VECTOR, FeedForward, ParamSpec, register_part
 from .linear import Linear
 
 
@@ -12,22 +12,42 @@ from .linear import Linear
 class DenseMLP(FeedForward):
     """``residual += act(h @ Wfc + bfc) @ Wproj + bproj`` (src/model.rs:462-473,485-487).
     ``activation`` is ``gelu_tanh`` (src/ops.rs:21-24), ``gelu_erf`` or ``none``; ``hidden`` is
-    a plain number, not derived from the width (src/config.rs:13)."""
+    a plain number, not derived from the width (src/config.rs:13).
+
+    ``xielu`` is an activation with two learned numbers ``p, q`` (the parameter ``act``):
+    ``z > 0: softplus(p) z^2 + z/2``; ``z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2``.
+    The product kernels' epilogues carry no learned numbers, so the first product hands out
+    fp32 rows and a pass of its own applies the activation to them."""
     graph_safe = True
     accepts_deferred_norm = True
+    can_overwrite = True
 
     def __init__(self, width: int, hidden: int, activation: str, bias: bool = True):
-        if activation not in ACTIVATIONS:
-            raise ValueError(f"unknown activation {activation!r} (have {sorted(ACTIVATIONS)})")
+        if activation not in ACTIVATIONS and activation not in ROW_ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r} "
+                             f"(have {sorted({**ACTIVATIONS, **ROW_ACTIVATIONS})})")
         self.width, self.hidden = int(width), int(hidden)
         self.activation = activation
-        self.act_code = ACTIVATIONS[activation]
+        self.learned = activation not in ACTIVATIONS
+        self.act_code = ROW_ACTIVATIONS[activation] if self.learned else ACTIVATIONS[activation]
         self.fc = Linear(self.width, self.hidden, bias)
         self.proj = Linear(self.hidden, self.width, bias)
+        self.act = None
 
     def children(self):
         return {"fc": self.fc, "proj": self.proj}
 
-    def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor) -> None:
-        mid = self.fc(ctx, h, act=self.act_code)
-        self.proj(ctx, mid, residual=residual)
+    def param_specs(self):
+        return {"act": ParamSpec((2,), VECTOR)} if self.learned else {}
+
+    def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
+        if self.learned:
+            z = self.fc(ctx, h, out_dtype=torch.float32)
+            mid = torch.empty(z.shape, device=z.device, dtype=ctx.rt.act_dtype)
+            ctx.ops.act_rows(z, 0, self.act_code, self.act, mid)
+        else:
+            mid = self.fc(ctx, h, act=self.act_code)
+        if accumulate:
+            self.proj(ctx, mid, residual=residual)
+        else:
+            self.proj(ctx, mid, out=residual)

@@ -52,3 +52,17 @@ class RMSNorm(Norm):
         out = torch.empty((n, self.width), device=x.device, dtype=ctx.rt.act_dtype)
         ctx.ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
+
+    def add_into(self, ctx, y, residual, then: "RMSNorm | None" = None, rounded: bool = False):
+        """``residual += norm(y)`` for a sublayer's fp32 result ``y``, in one pass over the rows
+        that can also hand out what the next reader of the stream wants: with ``then`` the
+        rows of ``then(residual)`` (the norm in front of the next sublayer), with ``rounded``
+        the stream's rows in the activation type.  Returns ``(then's rows or None, rounded
+        rows or None)``."""
+        act = ctx.rt.act_dtype
+        nxt = torch.empty(residual.shape, device=y.device, dtype=act) if then is not None else None
+        cast = torch.empty(residual.shape, device=y.device, dtype=act) if rounded else None
+        ctx.ops.rms_add(y, self.weight, self.eps, residual,
+                        then.weight if then is not None else None,
+                        then.eps if then is not None else 0.0, nxt, cast)
+        return nxt, cast

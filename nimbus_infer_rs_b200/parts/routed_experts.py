@@ -10,7 +10,8 @@ from .linear import Linear
 
 @register_part("ffn", "routed_experts")
 class RoutedExperts(FeedForward):
-    """``residual += sum_{e in chosen} s_e * down_e(act(gate_e h) * (up_e h))``.
+    """``residual += sum_{e in chosen} s_e * down_e(act(gate_e h) * (up_e h))``, or, with
+    ``gated=False``, ``s_e * down_e(act(up_e h))`` (experts of two matrices).
 
     ``s = softmax(router h)`` over all ``n_experts`` in fp32; the ``top`` experts with the
     largest scores are chosen per token (of equal scores the lower index); their weights are
@@ -29,7 +30,7 @@ class RoutedExperts(FeedForward):
     graph_safe = True
 
     def __init__(self, width: int, n_experts: int, top: int, hidden: int, activation: str = "silu",
-                 renormalize: bool = False, router_from_mixer: bool = False):
+                 renormalize: bool = False, router_from_mixer: bool = False, gated: bool = True):
         if activation not in GATE_ACTIVATIONS:
             raise ValueError(f"unknown activation {activation!r} (have {sorted(GATE_ACTIVATIONS)})")
         self.width, self.n_experts, self.top, self.hidden = int(width), int(n_experts), int(top), int(hidden)
@@ -39,6 +40,7 @@ class RoutedExperts(FeedForward):
         self.act_code = GATE_ACTIVATIONS[activation]
         self.renormalize = bool(renormalize)
         self.router_from_mixer = bool(router_from_mixer)
+        self.gated = bool(gated)
         self.router = None if self.router_from_mixer else Linear(self.width, self.n_experts, bias=False)
         self.gate = self.up = self.down = None
 
@@ -47,10 +49,16 @@ class RoutedExperts(FeedForward):
 
     def param_specs(self):
         e, f, d = self.n_experts, self.hidden, self.width
-        return {"gate": ParamSpec((e, f, d), MATRIX), "up": ParamSpec((e, f, d), MATRIX),
-                "down": ParamSpec((e, d, f), MATRIX)}
+        specs = {"up": ParamSpec((e, f, d), MATRIX), "down": ParamSpec((e, d, f), MATRIX)}
+        if self.gated:
+            specs["gate"] = ParamSpec((e, f, d), MATRIX)
+        return specs
 
-    def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor) -> None:
+    can_overwrite = True
+
+    def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
+        if not accumulate:
+            residual.zero_()
         lay, ops, dev = ctx.layout, ctx.ops, h.device
         n, top = lay.n_rows, self.top
         if self.router_from_mixer:
@@ -65,7 +73,10 @@ class RoutedExperts(FeedForward):
         place = torch.empty(n * top, device=dev, dtype=torch.int32)
         ops.moe_group(idx, self.n_experts, offsets, order, place)
         mid = torch.empty((n * top, self.hidden), device=dev, dtype=ctx.rt.act_dtype)
-        ops.moe_linear(h, order, top, offsets, self.gate, self.up, mid, self.act_code)
+        if self.gated:
+            ops.moe_linear(h, order, top, offsets, self.gate, self.up, mid, self.act_code)
+        else:
+            ops.moe_linear(h, order, top, offsets, self.up, None, mid, self.act_code)
         y = torch.empty((n * top, self.width), device=dev, dtype=torch.float32)
         ops.moe_linear(mid, None, 1, offsets, self.down, None, y)
         ops.moe_combine(y, place, weight, residual)

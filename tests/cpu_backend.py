@@ -16,11 +16,11 @@ class CpuBackend:
     def __init__(self):
         self.launches = 0
 
-    def embed_pos(self, tokens, pos, wte, wpe, out):
+    def embed_pos(self, tokens, pos, wte, wpe, out, scale=1.0):
         n = out.shape[0]
         tok = tokens[:n].long()
         valid = tok >= 0
-        x = wte[tok.clamp(min=0)].float()
+        x = wte[tok.clamp(min=0)].float() * scale
         if wpe is not None:
             x = x + wpe[pos[:n].long()].float()
         out.copy_(torch.where(valid[:, None], x, torch.zeros_like(x)))
@@ -47,6 +47,132 @@ class CpuBackend:
         if rows is not None:
             y = torch.where((rows[:n] >= 0)[:, None], y, torch.zeros_like(y))
         out.copy_(y.to(out.dtype))
+
+    def rms_add(self, y, gamma, eps, residual, next_gamma, next_eps, out_next, out_cast):
+        n = residual.shape[0]
+        v = y[:n] / torch.sqrt((y[:n] * y[:n]).mean(-1, keepdim=True) + eps) * gamma
+        residual += v
+        if out_next is not None:
+            x = residual
+            out_next.copy_((x / torch.sqrt((x * x).mean(-1, keepdim=True) + next_eps)
+                            * next_gamma).to(out_next.dtype))
+        if out_cast is not None:
+            out_cast.copy_(residual.to(out_cast.dtype))
+
+    def act_rows(self, x, x_col, act, params, out):
+        n, d = out.shape
+        z = x[:n, x_col:x_col + d].float()
+        if act == 5:
+            y = torch.tanh(z)
+        elif act == 6:
+            sp = torch.nn.functional.softplus
+            ap, an = sp(params[0]), 0.5 + sp(params[1])
+            neg = torch.clamp(z, max=0.0)
+            y = torch.where(z > 0, ap * z * z + 0.5 * z, an * (torch.expm1(neg) - neg) + 0.5 * z)
+        else:
+            raise ValueError(act)
+        out.copy_(y.to(out.dtype))
+
+    def gather_mul(self, g, table, tokens, out):
+        n = out.shape[0]
+        tok = tokens[:n].long()
+        e = table[tok.clamp(min=0)].float()
+        y = torch.where((tok >= 0)[:, None], g[:n].float() * e, torch.zeros_like(e))
+        out.copy_(y.to(out.dtype))
+
+    @staticmethod
+    def _entry(kv, plane, slot, index):
+        page = int(kv.block_table[slot, index // kv.page])
+        return plane[page, :, index % kv.page, :]
+
+    def qk_norm_rope_append(self, src, q_col, k_col, q_gamma, k_gamma, eps, freq, rot_dims,
+                            amplitude, layout, kv, n_heads, q_out, write):
+        d, G = kv.head_dim, kv.n_kv_heads
+        half = rot_dims // 2
+
+        def turn(x, pos):
+            if not rot_dims:
+                return x
+            ang = (torch.tensor(float(pos), dtype=torch.float32) * freq).float()
+            c, s = torch.cos(ang) * amplitude, torch.sin(ang) * amplitude
+            u, v = x[:, :half], x[:, half:rot_dims]
+            return torch.cat([u * c - v * s, v * c + u * s, x[:, rot_dims:]], dim=-1)
+
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                q_out[r].zero_()
+                continue
+            pos = int(layout.row_pos[r])
+            q = src[r, q_col:q_col + n_heads * d].float().view(n_heads, d)
+            k = src[r, k_col:k_col + G * d].float().view(G, d)
+            qn = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * q_gamma
+            kn = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * k_gamma
+            q_out[r] = turn(qn, pos).reshape(-1).to(q_out.dtype)
+            if write:
+                self._entry(kv, kv.k, slot, pos)[:] = turn(kn, pos).to(kv.k.dtype)
+                self._entry(kv, kv.v, slot, pos)[:] = k.to(kv.v.dtype)
+
+    def pool_blocks(self, layout, kv, blocks, pool):
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            pos = int(layout.row_pos[r])
+            if slot < 0 or (pos + 1) % pool:
+                continue
+            ks = torch.stack([self._entry(kv, kv.k, slot, j).float() for j in range(pos + 1 - pool, pos + 1)])
+            vs = torch.stack([self._entry(kv, kv.v, slot, j).float() for j in range(pos + 1 - pool, pos + 1)])
+            self._entry(blocks, blocks.k, slot, pos // pool)[:] = ks.mean(0).to(blocks.k.dtype)
+            self._entry(blocks, blocks.v, slot, pos // pool)[:] = vs.mean(0).to(blocks.v.dtype)
+
+    def attention_pooled(self, q, layout, kv, blocks, n_heads, sink, out, scale, window, pool):
+        d, G = kv.head_dim, kv.n_kv_heads
+        group = n_heads // G
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                out[r].zero_()
+                continue
+            pos = int(layout.row_pos[r])
+            lo = max(0, pos + 1 - window) if window > 0 else 0
+            keys = [self._entry(kv, kv.k, slot, j).float() for j in range(lo, pos + 1)]
+            vals = [self._entry(kv, kv.v, slot, j).float() for j in range(lo, pos + 1)]
+            if blocks is not None and window > 0 and pool > 0:
+                for b in range(max(0, (pos - window + 1) // pool)):
+                    keys.append(self._entry(blocks, blocks.k, slot, b).float())
+                    vals.append(self._entry(blocks, blocks.v, slot, b).float())
+            keys, vals = torch.stack(keys), torch.stack(vals)          # [n, G, d]
+            qr = q[r].float().view(n_heads, d)
+            for h in range(n_heads):
+                s = (keys[:, h // group] @ qr[h]) * scale
+                m = s.max() if sink is None else torch.maximum(s.max(), sink[h])
+                e = torch.exp(s - m)
+                den = e.sum() + (torch.exp(sink[h] - m) if sink is not None else 0.0)
+                out[r, h * d:(h + 1) * d] = ((e / den) @ vals[:, h // group]).to(out.dtype)
+
+    def delta_rule(self, fused, col_r, col_k, col_v, col_g, col_a, decay_logits, a_bias, norm_w,
+                   eps, decay_rate, key_eps, layout, state, n_heads, dim, out):
+        H, d = n_heads, dim
+        hd = H * d
+        for r in range(layout.n_rows):        # rows of a sequence come in order of position
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                out[r].zero_()
+                continue
+            row = fused[r].float()
+            rr = row[col_r:col_r + hd].view(H, d)
+            k = row[col_k:col_k + hd].view(H, d)
+            v = row[col_v:col_v + hd].view(H, d)
+            g = torch.sigmoid(row[col_g:col_g + hd])
+            a = torch.sigmoid(row[col_a:col_a + hd] + a_bias).view(H, d)
+            w = torch.exp(-decay_rate * torch.sigmoid(decay_logits[r].float())).view(H, d)
+            u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + key_eps)
+            S = state[slot].view(H, d, d)
+            removed = torch.einsum("hk,hkv->hv", u, S)
+            S.copy_(w[:, :, None] * S - (a * u)[:, :, None] * removed[:, None, :]
+                    + k[:, :, None] * v[:, None, :])
+            o = torch.einsum("hkv,hk->hv", S, rr)
+            o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps)
+            out[r] = (o.reshape(hd) * norm_w * g).to(out.dtype)
 
     def latent_append(self, src, col, gamma, eps, layout, kv):
         rank = kv.head_dim
@@ -124,6 +250,8 @@ class CpuBackend:
             for at in range(int(offsets[e]), int(offsets[e + 1])):
                 row = int(order[at]) // row_div if order is not None else at
                 v = w[e].float() @ x[row].float()
+                if w2 is None and act == 4:
+                    v = torch.clamp(v, min=0.0) ** 2
                 if w2 is not None:
                     if act == 3:
                         v = v * torch.sigmoid(v)
