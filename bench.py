@@ -289,7 +289,8 @@ def run_workload(engine, cfg, prompt_lens, n_new, hbm_gbs, windows=()):
 # ---------------------------------------------------------------------------------------------
 # --designs: Runesun beside GPT-2 at equal layer sizes
 # ---------------------------------------------------------------------------------------------
-DESIGN_PAIRS = (("runesun-2k", "gpt2-2k"), ("runesun-1k", "gpt2-1k"))
+DESIGN_PAIRS = {"runesun": (("runesun-2k", "gpt2-2k"), ("runesun-1k", "gpt2-1k")),
+                "rizitar": (("rizitar-2k", "gpt2-2k"), ("rizitar-1k", "gpt2-1k"))}
 
 
 class OpTimer:
@@ -298,7 +299,9 @@ class OpTimer:
     tensors it is given.  Kernels of a kind are added up."""
 
     KINDS = ("linear", "layernorm", "rmsnorm", "attention", "attention_latent", "latent_append",
-             "head_linear", "moe_route", "moe_group", "moe_linear", "moe_combine", "embed_pos")
+             "head_linear", "moe_route", "moe_group", "moe_linear", "moe_combine", "embed_pos",
+             "rms_add", "act_rows", "gather_mul", "qk_norm_rope_append", "pool_blocks",
+             "attention_pooled", "delta_rule")
 
     def __init__(self, ops):
         import torch
@@ -336,7 +339,8 @@ class OpTimer:
         if kind == "linear":
             return f"linear {a[1].shape[0]}x{a[1].shape[1]}"
         if kind == "moe_linear":
-            return "moe_linear gate+up" if a[5] is not None else "moe_linear down"
+            return "moe_linear gate+up" if a[5] is not None else (
+                "moe_linear up" if a[1] is not None else "moe_linear down")
         return kind
 
     def _work(self, kind, a, kw):
@@ -375,6 +379,35 @@ class OpTimer:
             return 4 * out.numel() + nb(out), 0
         if kind == "moe_combine":
             return nb(a[0]) + 2 * nb(a[3]), 0
+        if kind == "rms_add":
+            return nb(a[0], a[6], a[7]) + 2 * nb(a[3]), 0
+        if kind == "act_rows":
+            return 4 * a[4].numel() + nb(a[4]), 0
+        if kind == "gather_mul":
+            return nb(a[0], a[3]) + a[3].numel() * a[1].element_size(), 0
+        if kind == "qk_norm_rope_append":
+            lay, kv, heads, q = a[9], a[10], a[11], a[12]
+            width = (heads + kv.n_kv_heads) * kv.head_dim
+            return lay.n_tokens * (4 * width + 2 * kv.n_kv_heads * kv.head_dim * kv.k.element_size()) + nb(q), 0
+        if kind == "attention_pooled":
+            q, lay, kv, heads, window, pool = a[0], a[1], a[2], a[4], a[8], a[9]
+            elt, per_key = kv.k.element_size(), kv.n_kv_heads * kv.head_dim
+            width = heads * kv.head_dim
+
+            def seen(i):        # entries position i sees: its window and the blocks before it
+                w = min(i + 1, window) if window else i + 1
+                return w + (max(0, (i + 1 - window) // pool) if window and pool else 0)
+            pairs = sum(seen(i) for p, n in zip(lay.seq_pos0_host, lay.seq_lens) for i in range(p, p + n))
+            # every sequence's window and blocks once (a row's neighbours share them), queries, outputs
+            keys = sum(seen(p + n - 1) + (n - 1 if window else 0) for p, n in zip(lay.seq_pos0_host, lay.seq_lens))
+            return keys * per_key * 2 * elt + 2 * lay.n_tokens * width * elt, 4 * pairs * width
+        if kind == "delta_rule":
+            fused, lay, state, heads, dim, out = a[0], a[12], a[13], a[14], a[15], a[16]
+            hd = heads * dim
+            # five fp32 vectors and the decay's logits per token, the state of every sequence in
+            # and out; per token and head 6 dim^2 multiply-adds on the CUDA cores
+            return lay.n_tokens * 6 * hd * 4 + nb(out) + 2 * lay.n_seqs * hd * dim * 4, \
+                2 * 3 * lay.n_tokens * hd * dim
         return 0, 0
 
     def table(self, peaks):
@@ -439,7 +472,7 @@ def compare_designs(args, peaks):
     results = []
     launches = 0
     with ClockSampler() as clocks:
-        for pair in DESIGN_PAIRS:
+        for pair in DESIGN_PAIRS[args.design]:
             entry = {}
             for name in pair:
                 engine = Engine.random(name, seed=0, dtype="bfloat16", cache_tokens=66 * CONTEXT)
@@ -484,8 +517,10 @@ def main() -> int:
     ap.add_argument("--model", default=MODEL, choices=[MODEL, *OTHER_MODELS],
                     help="layer sizes (a preset); other than the default only with --only")
     ap.add_argument("--designs", action="store_true",
-                    help="instead of the headline: Runesun beside GPT-2 at equal layer sizes "
+                    help="instead of the headline: another design beside GPT-2 at equal layer sizes "
                          "(decode, prefill, per-kernel roofline fractions)")
+    ap.add_argument("--design", default="runesun", choices=sorted(DESIGN_PAIRS),
+                    help="with --designs: which design stands beside GPT-2")
     args = ap.parse_args()
 
     if args.impl == "reference":

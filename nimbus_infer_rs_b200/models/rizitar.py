@@ -60,7 +60,7 @@ def build_spec(cfg: RizitarConfig) -> ModelSpec:
             ffn = None
         elif isinstance(ff, DenseFFConfig):
             ffn = PartSpec("dense_mlp", {"width": D, "hidden": ff.ff, "activation": "xielu",
-                                         "bias": True})
+                                         "bias": "required"})
         else:
             ffn = PartSpec("routed_experts", {
                 "width": D, "n_experts": ff.experts, "top": ff.top, "hidden": ff.ff,

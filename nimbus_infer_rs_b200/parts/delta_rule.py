@@ -43,7 +43,7 @@ class DeltaRule(Mixer):
         # rows of zeros fill it up to a multiple of 8 outputs (fp32 rows on 32-byte boundaries)
         self.proj_outputs = -(-(self.col_w1 + self.decay_rank) // 8) * 8
         self.proj = Linear(self.width, self.proj_outputs, bias=False)
-        self.decay_up = Linear(self.decay_rank, self.inner, bias=True)      # W2 and w0
+        self.decay_up = Linear(self.decay_rank, self.inner, bias="required")      # W2 and w0
         self.out = Linear(self.inner, self.width, bias=False)
         self.a_bias = self.norm = None
 

@@ -17,10 +17,13 @@ class Linear(Part):
     family = "linear"
     kind = "linear"
 
-    def __init__(self, in_features: int, out_features: int, bias: bool = True):
+    def __init__(self, in_features: int, out_features: int, bias: bool | str = True):
+        """``bias``: ``False`` none, ``True`` one that a weight file may leave out, ``"required"``
+        one that it must hold."""
         self.in_features = int(in_features)
         self.out_features = int(out_features)
         self.has_bias = bool(bias)
+        self.bias_required = bias == "required"
         self.weight: torch.Tensor | None = None
         self.bias: torch.Tensor | None = None
 
@@ -28,7 +31,7 @@ class Linear(Part):
         specs = {"weight": ParamSpec((self.out_features, self.in_features), MATRIX)}
         if self.has_bias:
             # a bias is optional per tensor (src/engine.rs:153-161)
-            specs["bias"] = ParamSpec((self.out_features,), VECTOR, optional=True)
+            specs["bias"] = ParamSpec((self.out_features,), VECTOR, optional=not self.bias_required)
         return specs
 
     def __call__(self, ctx, x: torch.Tensor, *, out: torch.Tensor | None = None,

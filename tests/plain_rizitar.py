@@ -79,11 +79,41 @@ def rotate(x, positions, rot):
 
 
 # ------------------------------------------------------------------------------ mixers
+def seen_attention(q, k, v, scale, size, P, sink):
+    """q [T, H, d], k and v [T, G, d] as the cache holds them: position ``i`` sees the tokens
+    ``j`` with ``0 <= i - j < size`` (all earlier ones if ``size`` is 0) and, for every block of
+    ``P`` tokens that lies wholly before that window (``bP + P - 1 <= i - size``), the mean of
+    its keys and the mean of its values; one softmax over both, whose denominator also holds
+    ``exp(sink_h)``.  Returns [T, H, d]."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[-1], dtype=F64)
+    for i in range(T):
+        lo = max(0, i - size + 1) if size > 0 else 0
+        keys, vals = [k[lo:i + 1]], [v[lo:i + 1]]
+        if size > 0 and P > 0:
+            b = 0
+            while b * P + P - 1 <= i - size:
+                keys.append(k[b * P:b * P + P].mean(0, keepdim=True))
+                vals.append(v[b * P:b * P + P].mean(0, keepdim=True))
+                b += 1
+        kk, vv = torch.cat(keys), torch.cat(vals)              # [n, G, d]
+        for hh in range(H):
+            g = hh // (H // G)
+            s = (kk[:, g] @ q[i, hh]) * scale
+            sk = None if sink is None else sink[hh]
+            m = s.max() if sk is None else torch.maximum(s.max(), sk)
+            e = torch.exp(s - m)
+            den = e.sum() + (torch.exp(sk - m) if sk is not None else 0.0)
+            out[i, hh] = (e / den) @ vv[:, g]
+    return out
+
+
 def pooled_window_attention(h, w, mx, eps):
     """The attention mixer on normed rows ``h`` [T, D]; ``w``: the layer's ``mix.*`` tensors by
     their short names; ``mx``: the layer's mixer object of config.json."""
     T = h.shape[0]
-    H, G, d = int(mx["heads"]), int(mx["kv_heads"]), int(mx["dim"])
+    H, G, d = int(mx["heads"]), int(mx.get("kv_heads", mx["heads"])), int(mx["dim"])
     q = (h @ w["q"].T).view(T, H, d)
     k = (h @ w["k"].T).view(T, G, d)
     v = k.clone()                                    # the values are the keys as projected
@@ -92,29 +122,30 @@ def pooled_window_attention(h, w, mx, eps):
     pos = torch.arange(T)
     q, k = rotate(q, pos, mx.get("rot")), rotate(k, pos, mx.get("rot"))
     mask = mx.get("mask") or {}
-    size = int(mask.get("size", 0))
-    P = int(mask.get("pool", 0))
-    out = torch.zeros(T, H, v.shape[-1], dtype=F64)
-    for i in range(T):
-        lo = max(0, i - size + 1) if size > 0 else 0
-        keys, vals = [k[lo:i + 1]], [v[lo:i + 1]]
-        if size > 0 and P > 0:
-            for b in range(T):
-                if b * P + P - 1 <= i - size:
-                    keys.append(k[b * P:b * P + P].mean(0, keepdim=True))
-                    vals.append(v[b * P:b * P + P].mean(0, keepdim=True))
-                else:
-                    break
-        kk, vv = torch.cat(keys), torch.cat(vals)              # [n, G, d]
-        for hh in range(H):
-            g = hh // (H // G)
-            s = (kk[:, g] @ q[i, hh]) * float(mx["scale"])
-            sink = w["sink"][hh] if "sink" in w else None
-            m = s.max() if sink is None else torch.maximum(s.max(), sink)
-            e = torch.exp(s - m)
-            den = e.sum() + (torch.exp(sink - m) if sink is not None else 0.0)
-            out[i, hh] = (e / den) @ vv[:, g]
+    out = seen_attention(q, k, v, float(mx["scale"]), int(mask.get("size", 0)),
+                         int(mask.get("pool") or 0), w.get("sink"))
     return out.reshape(T, -1) @ w["o"].T
+
+
+def delta_recurrence(r, k, v, decay, a, S=None):
+    """r, k, v, decay, a: [T, H, d].  From the state ``S`` [H, d, d] (key channel, value channel;
+    zeros if ``None``): ``S <- diag(decay) S - (a * u)(u^T S) + k v^T`` with the unit key ``u``,
+    both subtracted terms reading the old state, then ``o = S^T r``.  Returns (o [T, H, d], S)."""
+    T, H, d = r.shape
+    u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    S = torch.zeros(H, d, d, dtype=F64) if S is None else S.clone()
+    o = torch.zeros(T, H, d, dtype=F64)
+    for t in range(T):
+        old = S
+        removed = torch.einsum("hk,hkv->hv", u[t], old)            # u^T S
+        S = decay[t][:, :, None] * old - (a[t] * u[t])[:, :, None] * removed[:, None, :] \
+            + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hkv,hk->hv", S, r[t])
+    return o, S
+
+
+def decay_of(logits):
+    return torch.exp(-math.exp(-0.5) * torch.sigmoid(logits))
 
 
 def general_delta(h, w, mx, eps):
@@ -124,18 +155,9 @@ def general_delta(h, w, mx, eps):
     r = (h @ w["r"].T).view(T, H, d)
     k = (h @ w["k"].T).view(T, H, d)
     v = (h @ w["v"].T).view(T, H, d)
-    decay = torch.exp(-math.exp(-0.5) * torch.sigmoid(torch.tanh(h @ w["w1"].T) @ w["w2"].T + w["w0"]))
-    decay = decay.view(T, H, d)
+    decay = decay_of(torch.tanh(h @ w["w1"].T) @ w["w2"].T + w["w0"]).view(T, H, d)
     a = torch.sigmoid(h @ w["a"].T + w["a.b"]).view(T, H, d)
-    u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-    S = torch.zeros(H, d, d, dtype=F64)                # [head, key channel, value channel]
-    o = torch.zeros(T, H, d, dtype=F64)
-    for t in range(T):
-        old = S
-        removed = torch.einsum("hk,hkv->hv", u[t], old)            # u^T S
-        S = decay[t][:, :, None] * old - (a[t] * u[t])[:, :, None] * removed[:, None, :] \
-            + k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hkv,hk->hv", S, r[t])
+    o, _ = delta_recurrence(r, k, v, decay, a)
     o = rms_unit(o, eps).reshape(T, H * d) * w["norm"]
     o = o * torch.sigmoid(h @ w["g"].T)
     return o @ w["o"].T
@@ -155,17 +177,23 @@ def route(h, router, top):
     return order, torch.gather(s, 1, order)
 
 
-def moe_ff(h, w, ff, choice=None):
+def moe_ff(h, w, ff, follow=None, margin=0.0):
+    """``follow``: [T, top] experts that someone else chose.  Where that choice differs from the
+    one made here and the router's logits of the last expert in and the first one out are
+    closer than ``margin`` (a close call that rounding may settle either way), it is followed."""
     E, top = int(ff["router"]["experts"]), int(ff["router"]["top"])
+    z = h @ w["router"].T
+    s = torch.softmax(z, dim=-1)
     order, score = route(h, w["router"], top)
-    if choice is not None:                      # a caller that settles near-ties its own way
-        order = choice
-        score = torch.gather(torch.softmax(h @ w["router"].T, dim=-1), 1, order)
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=F64)
     for t in range(h.shape[0]):
-        for j in range(top):
-            e = int(order[t, j])
-            out[t] += score[t, j] * (relu_squared(h[t] @ w[f"e{e}.up"].T) @ w[f"e{e}.down"].T)
+        mine = order[t]
+        if follow is not None and top < E and set(follow[t].tolist()) != set(mine.tolist()):
+            ranked = torch.sort(z[t], descending=True, stable=True).values
+            if float(ranked[top - 1] - ranked[top]) < margin:
+                mine = follow[t]
+        for e in mine.tolist():
+            out[t] += s[t, e] * (relu_squared(h[t] @ w[f"e{e}.up"].T) @ w[f"e{e}.down"].T)
     return out
 
 
@@ -182,16 +210,17 @@ def _sub(tensors, prefix):
     return {k[n:]: v.to(F64) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg: dict, tensors: dict, tokens, return_layers: bool = False, choices=None):
+def forward(cfg: dict, tensors: dict, tokens, return_layers: bool = False, routed=None,
+            margin: float = 0.0):
     """Logits [T, vocab] of one sequence (float64); with ``return_layers`` also the stream after
-    every layer [layers, T, D].  ``choices``: ``{layer: [T, top] expert indices}`` to use
-    instead of the router's own order."""
+    every layer [layers, T, D].  ``routed``: per layer with routed experts, in order, the
+    [T, top] experts someone else chose (see :func:`moe_ff`)."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     eps = float(cfg["norm"]["eps"])
     embed = tensors["embed"].to(F64)
-    x = embed[tokens] * float(cfg["embedding"]["scale"])
+    x = embed[tokens] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     side_dim = int(cfg["token_side"]["dim"]) if cfg.get("token_side") else 0
-    after = []
+    after, n_routed = [], 0
     for i, layer in enumerate(cfg["layers"]):
         w = _sub(tensors, f"l{i}.")
         mix = _sub(tensors, f"l{i}.mix.")
@@ -210,7 +239,8 @@ def forward(cfg: dict, tensors: dict, tokens, return_layers: bool = False, choic
             if ff["kind"] == "dense":
                 y = dense_ff(h, mlp)
             else:
-                y = moe_ff(h, mlp, ff, None if choices is None else choices.get(i))
+                y = moe_ff(h, mlp, ff, None if routed is None else routed[n_routed], margin)
+                n_routed += 1
             x = x + rms_norm(y, w["norm2b"], eps)
         if side_dim:
             x = x + token_side(x, tokens, _sub(tensors, f"l{i}.side."),
