@@ -49,12 +49,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int HD, typename TOut>
+// EXTRA: the kernel also takes a second paged store of pooled blocks (entry b = the mean key
+// and mean value of tokens b*pool .. b*pool+pool-1; row i sees it once b*pool + pool - 1 <=
+// i - window) whose pages are walked before the window's, and a sink per head: one more term
+// exp(sink_h) of the softmax's denominator, without a key, a value or the score scale.
+template <int HD, typename TOut, bool EXTRA>
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
                          const int* __restrict__ cu_rows, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_pos0, NbPagedKV kv, int group,
-                         TOut* __restrict__ out, int out_stride, float scale, int window) {
+                         TOut* __restrict__ out, int out_stride, float scale, int window,
+                         NbPagedKV blocks, int pool, const float* __restrict__ sink) {
   constexpr int ROW = HD + 8;              // padded row (elements): ldmatrix without conflicts
   constexpr int KS = HD / 16;              // k-steps of the score product
   constexpr int NT = HD / 8;               // n-tiles of the value product
@@ -77,11 +82,18 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
   const int first_key = (window > 0) ? max(0, pos0 + q0 + 1 - window) : 0;
   const int p_begin = first_key / PAGE_TOKENS, p_end = last_pos / PAGE_TOKENS + 1;
   const int* table = kv.block_table + (size_t)slot * kv.max_pages;
+  // blocks the tile's last row sees, and their pages: walked first, as units 0 .. n_bpages - 1
+  const int nb_tile = (EXTRA && pool > 0 && window > 0 && blocks.k != nullptr)
+                          ? max(0, (last_pos + 1 - window) / pool) : 0;
+  const int n_bpages = (nb_tile + PAGE_TOKENS - 1) / PAGE_TOKENS;
+  const int* btable = (EXTRA && n_bpages > 0) ? blocks.block_table + (size_t)slot * blocks.max_pages : nullptr;
+  const int n_units = n_bpages + (p_end - p_begin);
 
-  auto issue = [&](int page_idx, int stage) {
-    const int page_id = table[page_idx];
-    const bf16* ksrc = (const bf16*)kv.k + ((size_t)page_id * kv.n_kv_heads + kvh) * PAGE_TOKENS * HD;
-    const bf16* vsrc = (const bf16*)kv.v + ((size_t)page_id * kv.n_kv_heads + kvh) * PAGE_TOKENS * HD;
+  auto issue = [&](int unit, int stage) {
+    const bool blk = EXTRA && unit < n_bpages;
+    const int page_id = blk ? btable[unit] : table[p_begin + unit - n_bpages];
+    const bf16* ksrc = (const bf16*)(blk ? blocks.k : kv.k) + ((size_t)page_id * kv.n_kv_heads + kvh) * PAGE_TOKENS * HD;
+    const bf16* vsrc = (const bf16*)(blk ? blocks.v : kv.v) + ((size_t)page_id * kv.n_kv_heads + kvh) * PAGE_TOKENS * HD;
     bf16* kdst = kv_s + (size_t)stage * 2 * PAGE_TOKENS * ROW;
     bf16* vdst = kdst + PAGE_TOKENS * ROW;
     constexpr int CPR = HD / 8;   // 16-byte chunks per row
@@ -92,7 +104,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
     }
     cp_async_commit();
   };
-  issue(p_begin, 0);
+  issue(0, 0);
 
   // the query tile: rows beyond the sequence are zero
   {
@@ -121,11 +133,16 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
   const float sl2 = scale * 1.4426950408889634f;    // scores in units of log2(e)
   const int qpos_a = pos0 + q0 + warp * 16 + g;     // absolute position of row g
   const int qpos_b = qpos_a + 8;                    // ... and of row g + 8
+  // blocks each of the two rows sees
+  const int nb_a = (EXTRA && nb_tile > 0 && qpos_a + 1 >= window) ? (qpos_a + 1 - window) / pool : 0;
+  const int nb_b = (EXTRA && nb_tile > 0 && qpos_b + 1 >= window) ? (qpos_b + 1 - window) / pool : 0;
 
-  for (int p = p_begin; p < p_end; ++p) {
-    const int stage = (p - p_begin) & 1;
-    if (p + 1 < p_end) {
-      issue(p + 1, stage ^ 1);
+  for (int u = 0; u < n_units; ++u) {
+    const int stage = u & 1;
+    const bool blk = EXTRA && u < n_bpages;
+    const int p = p_begin + u - n_bpages;           // the page of tokens (when not blocks)
+    if (u + 1 < n_units) {
+      issue(u + 1, stage ^ 1);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
@@ -136,7 +153,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
     // Rows of the last page after the newest key hold whatever an earlier owner of the page
     // left there.  Their probabilities are zero, but zero times a non-finite value is not: the
     // value rows are cleared in the staged copy (masked scores are replaced, not multiplied).
-    const int tail_row = last_pos + 1 - p * PAGE_TOKENS;
+    const int tail_row = blk ? nb_tile - u * PAGE_TOKENS : last_pos + 1 - p * PAGE_TOKENS;
     if (tail_row < PAGE_TOKENS) {   // uniform over the CTA
       constexpr int CPR = HD / 8;
       for (int i = tid; i < (PAGE_TOKENS - tail_row) * CPR; i += THREADS) {
@@ -167,7 +184,19 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
     // row of this warp (and needs no window) is visible to all of its rows: no comparisons.
     const int j0 = p * PAGE_TOKENS;
     float mx[2] = {-INFINITY, -INFINITY};
-    if (window <= 0 && j0 + PAGE_TOKENS - 1 <= pos0 + q0 + warp * 16) {
+    if (blk) {
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int b = u * PAGE_TOKENS + n * 8 + t * 2 + (j & 1);
+          const bool ok = b < ((j < 2) ? nb_a : nb_b);
+          const float v = ok ? sc[n][j] * sl2 : -INFINITY;
+          sc[n][j] = v;
+          mx[j >> 1] = fmaxf(mx[j >> 1], v);
+        }
+      }
+    } else if (window <= 0 && j0 + PAGE_TOKENS - 1 <= pos0 + q0 + warp * 16) {
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
 #pragma unroll
@@ -239,6 +268,20 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
+  if (EXTRA && sink != nullptr) {
+    const float s2 = sink[h] * 1.4426950408889634f;   // like the scores, in units of log2(e)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float m_f = fmaxf(m_run[r], s2);
+      const float fix = (m_run[r] == -INFINITY) ? 0.0f : nb_exp2(m_run[r] - m_f);
+      l_run[r] = l_run[r] * fix + nb_exp2(s2 - m_f);
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        o[n][2 * r] *= fix;
+        o[n][2 * r + 1] *= fix;
+      }
+    }
+  }
   const float inv_a = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f;
   const float inv_b = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
   const int ra = warp * 16 + g, rb = ra + 8;
@@ -258,19 +301,20 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
   }
 }
 
-template <int HD, typename TOut>
+template <int HD, typename TOut, bool EXTRA = false>
 int launch(const void* q, int q_stride, int q_col, const int* cu_rows, const int* seq_slot,
            const int* seq_pos0, const NbPagedKV& kv, int n_heads, void* out, int out_stride,
-           float scale, int window, int n_seqs, int max_q_len, cudaStream_t stream) {
+           float scale, int window, int n_seqs, int max_q_len, cudaStream_t stream,
+           const NbPagedKV& blocks = NbPagedKV{}, int pool = 0, const float* sink = nullptr) {
   constexpr int ROW = HD + 8;
   const size_t smem = (size_t)(BLOCK_Q + 4 * PAGE_TOKENS) * ROW * sizeof(bf16);
-  auto kern = attention_prefill_kernel<HD, TOut>;
+  auto kern = attention_prefill_kernel<HD, TOut, EXTRA>;
   if (smem > 48 * 1024)
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((max_q_len + BLOCK_Q - 1) / BLOCK_Q, n_heads, n_seqs);
   kern<<<grid, THREADS, smem, stream>>>((const bf16*)q, q_stride, q_col, cu_rows, seq_slot,
                                         seq_pos0, kv, n_heads / kv.n_kv_heads, (TOut*)out,
-                                        out_stride, scale, window);
+                                        out_stride, scale, window, blocks, pool, sink);
   return 0;
 }
 
@@ -316,5 +360,43 @@ NB_EXPORT int nb_attention_prefill(const void* q, int dtype, int q_stride, int q
 #undef NB_HD
   if (rc) return rc;
   NB_CHECK_LAUNCH("attention_prefill");
+  return 0;
+}
+
+// The same walk with pooled blocks before the window and a sink (see EXTRA above).  bk, bv,
+// b_table: the paged store of blocks (null: none); sink: fp32 [n_heads] or null.  Steps of one
+// row per sequence run it too (a tile with one row).
+NB_EXPORT int nb_attention_pooled_mma(const void* q, int q_stride, int q_col, const int* cu_rows,
+                                      const int* seq_slot, const int* seq_pos0, const void* k_cache,
+                                      const void* v_cache, const int* block_table, int max_pages,
+                                      const void* bk, const void* bv, const int* b_table,
+                                      int b_max_pages, int page, int n_heads, int n_kv_heads,
+                                      int head_dim, const float* sink, void* out, int out_dtype,
+                                      int out_stride, float scale, int window, int pool, int n_seqs,
+                                      int max_q_len, cudaStream_t stream) {
+  if (n_seqs == 0 || max_q_len == 0) return 0;
+  NB_REQUIRE(nb_attention_prefill_supported(NB_BF16, head_dim, n_heads, n_kv_heads, page, q_stride, q_col),
+             NB_ERR_UNSUPPORTED,
+             "attention_pooled_mma: unsupported shape (head size %d, %d/%d heads, row pitch %d)",
+             head_dim, n_heads, n_kv_heads, q_stride);
+  NB_REQUIRE(n_seqs <= 65535 && n_heads <= 65535, NB_ERR_UNSUPPORTED,
+             "attention_pooled_mma: grid too large");
+  NB_REQUIRE((uintptr_t)q % 16 == 0 && window >= 0 && pool >= 0, NB_ERR_UNSUPPORTED,
+             "attention_pooled_mma: unaligned queries or a negative window");
+  NbPagedKV kv{(void*)k_cache, (void*)v_cache, block_table, max_pages, page, n_kv_heads, head_dim};
+  NbPagedKV blocks{(void*)bk, (void*)bv, b_table, b_max_pages, page, n_kv_heads, head_dim};
+  int rc = NB_ERR_UNSUPPORTED;
+#define NB_HD(HD_)                                                                             \
+  case HD_:                                                                                    \
+    rc = out_dtype == NB_F32                                                                   \
+             ? launch<HD_, float, true>(q, q_stride, q_col, cu_rows, seq_slot, seq_pos0, kv, n_heads, out, out_stride, scale, window, n_seqs, max_q_len, stream, blocks, pool, sink) \
+             : launch<HD_, bf16, true>(q, q_stride, q_col, cu_rows, seq_slot, seq_pos0, kv, n_heads, out, out_stride, scale, window, n_seqs, max_q_len, stream, blocks, pool, sink); \
+    break;
+  switch (head_dim) {
+    NB_HD(16) NB_HD(32) NB_HD(48) NB_HD(64) NB_HD(96) NB_HD(128)
+  }
+#undef NB_HD
+  if (rc) return rc;
+  NB_CHECK_LAUNCH("attention_pooled_mma");
   return 0;
 }

@@ -12,6 +12,10 @@
 //   s_j <- w * s_j - (a*u) (u . s_j) + k v_j,     o_j = s_j . r.
 // A CTA takes one (sequence, head).  Column j lives in the registers of LPC = 4 neighbouring
 // lanes, a quarter of the key channels each; the two dot products finish with two shuffles.
+// The channels are dealt to the four lanes in groups of four (lane q has channels 16 g + 4 q ..
+// 16 g + 4 q + 3 for g = 0, 1, ...), so that the four lanes of a column read 64 consecutive
+// bytes of a shared-memory vector with one 16-byte load each: no bank conflicts, and the other
+// seven columns of the warp get the same bytes by broadcast.
 // Tokens are taken CHUNK at a time: all threads prepare the chunk's vectors (w, a*u, u, k, r, v)
 // in shared memory, then every thread walks the chunk's tokens in order without a barrier, then
 // all threads norm, gate and store the chunk's outputs.  The state is read from the sequence's
@@ -62,12 +66,13 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
   if (slot < 0 || row1 <= row0) return;
 
   const int col = tid / LPC, q = tid % LPC;     // this thread's column and quarter of the keys
-  const int kbase = q * KPL;
+  // the key channel of this thread's i-th state value
+  auto channel = [q](int i) { return (((i >> 2) * LPC + q) << 2) + (i & 3); };
   float* st = state + ((size_t)slot * n_heads + h) * d * d;
   float S[KPL];
 #pragma unroll
   for (int i = 0; i < KPL; ++i) {
-    const int k = kbase + i;
+    const int k = channel(i);
     S[i] = (k < d && col < d) ? st[(size_t)k * d + col] : 0.0f;
   }
 
@@ -106,22 +111,35 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
     __syncthreads();
     // ---- the recurrence: every thread walks the chunk's tokens in order
     for (int c = 0; c < nc; ++c) {
-      const float* wc = w_s + c * DP + kbase;
-      const float* auc = au_s + c * DP + kbase;
-      const float* uc = u_s + c * DP + kbase;
-      const float* kc = k_s + c * DP + kbase;
-      const float* rc = r_s + c * DP + kbase;
+      const float4* w4 = reinterpret_cast<const float4*>(w_s + c * DP) + q;
+      const float4* au4 = reinterpret_cast<const float4*>(au_s + c * DP) + q;
+      const float4* u4 = reinterpret_cast<const float4*>(u_s + c * DP) + q;
+      const float4* k4 = reinterpret_cast<const float4*>(k_s + c * DP) + q;
+      const float4* r4 = reinterpret_cast<const float4*>(r_s + c * DP) + q;
       const float vj = v_s[c * DP + col];
       float rem = 0.0f;
 #pragma unroll
-      for (int i = 0; i < KPL; ++i) rem = fmaf(uc[i], S[i], rem);
+      for (int g = 0; g < KPL / 4; ++g) {
+        const float4 uu = u4[g * LPC];
+        rem = fmaf(uu.x, S[4 * g], rem);
+        rem = fmaf(uu.y, S[4 * g + 1], rem);
+        rem = fmaf(uu.z, S[4 * g + 2], rem);
+        rem = fmaf(uu.w, S[4 * g + 3], rem);
+      }
       rem += __shfl_xor_sync(0xffffffffu, rem, 1);
       rem += __shfl_xor_sync(0xffffffffu, rem, 2);
       float o = 0.0f;
 #pragma unroll
-      for (int i = 0; i < KPL; ++i) {
-        S[i] = fmaf(kc[i], vj, fmaf(wc[i], S[i], -auc[i] * rem));
-        o = fmaf(S[i], rc[i], o);
+      for (int g = 0; g < KPL / 4; ++g) {
+        const float4 ww = w4[g * LPC], aa = au4[g * LPC], kk = k4[g * LPC], rr = r4[g * LPC];
+        S[4 * g] = fmaf(kk.x, vj, fmaf(ww.x, S[4 * g], -aa.x * rem));
+        S[4 * g + 1] = fmaf(kk.y, vj, fmaf(ww.y, S[4 * g + 1], -aa.y * rem));
+        S[4 * g + 2] = fmaf(kk.z, vj, fmaf(ww.z, S[4 * g + 2], -aa.z * rem));
+        S[4 * g + 3] = fmaf(kk.w, vj, fmaf(ww.w, S[4 * g + 3], -aa.w * rem));
+        o = fmaf(S[4 * g], rr.x, o);
+        o = fmaf(S[4 * g + 1], rr.y, o);
+        o = fmaf(S[4 * g + 2], rr.z, o);
+        o = fmaf(S[4 * g + 3], rr.w, o);
       }
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
@@ -149,7 +167,7 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
   }
 #pragma unroll
   for (int i = 0; i < KPL; ++i) {
-    const int k = kbase + i;
+    const int k = channel(i);
     if (k < d && col < d) st[(size_t)k * d + col] = S[i];
   }
 }

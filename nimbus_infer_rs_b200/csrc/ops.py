@@ -665,6 +665,22 @@ class CudaBackend:
             raise KernelError("attention_pooled: shapes do not agree")
         if sink is not None:
             _check(sink, "sink", torch.float32, 1)
+        if self.use_mma and q.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16 \
+                and self.lib.nb_attention_prefill_supported(1, d, n_heads, kv.n_kv_heads, kv.page,
+                                                            q.shape[1], 0):
+            # bfloat16 on the tensor cores (mma.sync), prompts and one-token steps alike: tiles
+            # of 64 query rows, the pages of pooled blocks walked before the window's
+            self._call("nb_attention_pooled_mma", _ptr(q), q.shape[1], 0, _ptr(layout.cu_rows),
+                       _ptr(layout.seq_slot), _ptr(layout.seq_pos0), _ptr(kv.k), _ptr(kv.v),
+                       _ptr(kv.block_table), kv.block_table.shape[1],
+                       _ptr(blocks.k if blocks is not None else None),
+                       _ptr(blocks.v if blocks is not None else None),
+                       _ptr(blocks.block_table if blocks is not None else None),
+                       blocks.block_table.shape[1] if blocks is not None else 0, kv.page, n_heads,
+                       kv.n_kv_heads, d, _ptr(sink), _ptr(out), dtype_code(out.dtype), out.shape[1],
+                       float(scale), int(window), int(pool), layout.n_seqs, layout.max_q_len,
+                       self._stream())
+            return
         self._call("nb_attention_pooled", _ptr(q), dtype_code(q.dtype), _ptr(layout.row_slot),
                    _ptr(layout.row_pos), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table),
                    kv.block_table.shape[1], _ptr(blocks.k if blocks is not None else None),

@@ -55,6 +55,7 @@ SIGNATURES = {
     "nb_gather_mul": "ppippiiip",
     "nb_qk_norm_rope_append": "piiippfpifpppippipiiiiiiip",
     "nb_pool_blocks": "pppppipppiiiiiiip",
+    "nb_attention_pooled_mma": "piippppppipppiiiiippiifiiiip",
     "nb_attention_pooled": "pipppppipppiiiiiippifiiip",
     "nb_delta_rule_supported": "i",
     "nb_delta_rule": "piiiiiipppfffppppiiiiip",
