@@ -10,18 +10,20 @@
 //
 // The columns of S are independent of one another: column j follows
 //   s_j <- w * s_j - (a*u) (u . s_j) + k v_j,     o_j = s_j . r.
-// A CTA takes one (sequence, head).  Column j lives in the registers of LPC = 4 neighbouring
-// lanes, a quarter of the key channels each; the two dot products finish with two shuffles.
-// The channels are dealt to the four lanes in groups of four (lane q has channels 16 g + 4 q ..
-// 16 g + 4 q + 3 for g = 0, 1, ...), so that the four lanes of a column read 64 consecutive
-// bytes of a shared-memory vector with one 16-byte load each: no bank conflicts, and the other
-// seven columns of the warp get the same bytes by broadcast.
-// Tokens are taken CHUNK at a time: all threads prepare the chunk's vectors (w, a*u, u, k, r, v)
-// in shared memory, then every thread walks the chunk's tokens in order without a barrier, then
-// all threads norm, gate and store the chunk's outputs.  The state is read from the sequence's
-// state row before the first token of the step and written back after the last, so a sequence
-// may be cut into steps anywhere: the arithmetic per token does not depend on the cut, nor on
-// what else is in the batch.
+// A CTA of 256 threads takes COLS = 256 / LPC columns of one (sequence, head); the CTAs of a
+// head share nothing.  Column j lives in the registers of LPC neighbouring lanes, DP / LPC key
+// channels each; the two dot products finish with log2(LPC) shuffles.  The channels are dealt to
+// the lanes in groups of four (lane q has channels 4 LPC g + 4 q .. + 3 for g = 0, 1, ...), so
+// that the lanes of a column read consecutive 16-byte pieces of a shared-memory vector: no bank
+// conflicts, and the other columns of the warp get the same bytes by broadcast.
+// Tokens are taken CHUNK at a time: all threads prepare the chunk's vectors (w, a*u, u, k, r and
+// the CTA's part of v) in shared memory, a warp per token with one trip to memory; then every
+// thread walks the chunk's tokens in order without a barrier; then the chunk's o goes out in
+// fp32.  A second kernel norms each head's o, applies weight and gate and writes the output type
+// (the norm needs all of a head's columns).  The state is read from the sequence's state row
+// before the first token of the step and written back after the last, so a sequence may be cut
+// into steps anywhere: the arithmetic per token does not depend on the cut, nor on what else is
+// in the batch.
 //
 // A decode step (one token per sequence) is the same kernel with a chunk of one token: it reads
 // and writes the state once, which is all the memory traffic there is.
@@ -29,43 +31,39 @@
 
 namespace {
 
-constexpr int LPC = 4;       // lanes per column of the state
+constexpr int THREADS = 256;
+constexpr int NW = THREADS / 32;
 constexpr int CHUNK = 16;    // tokens prepared at a time
 
-template <int DP, typename TOut>
-__global__ void __launch_bounds__(LPC * DP)
-delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_v, int col_g,
-                  int col_a, const float* decay_logits, const float* __restrict__ a_bias,
-                  const float* __restrict__ norm_w, float eps, float rate, float key_eps,
-                  const int* cu_rows, const int* seq_slot, float* state, TOut* out, int n_heads,
-                  int d, int n_seqs, int n_rows) {
+template <int DP, int LPC>
+__global__ void __launch_bounds__(THREADS)
+delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_v, int col_a,
+                  const float* decay_logits, const float* __restrict__ a_bias, float rate,
+                  float key_eps, const int* cu_rows, const int* seq_slot, float* state,
+                  float* o_raw, int n_heads, int d) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
   constexpr int KPL = DP / LPC;                 // key channels per lane
-  constexpr int THREADS = LPC * DP;
-  constexpr int NW = THREADS / 32;
+  constexpr int COLS = THREADS / LPC;           // columns of the state per CTA
+  constexpr int KIT = DP / 32;                  // key channels per lane of a preparing warp
+  static_assert(KPL % 4 == 0 && KPL >= 4, "a lane takes its channels four at a time");
   extern __shared__ __align__(16) float sm[];
   float* w_s = sm;                              // [CHUNK][DP] each
   float* au_s = w_s + CHUNK * DP;
   float* u_s = au_s + CHUNK * DP;
   float* k_s = u_s + CHUNK * DP;
   float* r_s = k_s + CHUNK * DP;
-  float* v_s = r_s + CHUNK * DP;
-  float* o_s = v_s + CHUNK * DP;
+  float* v_s = r_s + CHUNK * DP;                // [CHUNK][COLS]
+  float* o_s = v_s + CHUNK * COLS;              // [CHUNK][COLS]
 
-  const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS, tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const int hd = n_heads * d;
-
-  if (seq == 0) {   // padding rows after the last sequence give zeros
-    for (int r = cu_rows[n_seqs]; r < n_rows; ++r)
-      for (int i = tid; i < d; i += THREADS) out[(size_t)r * hd + h * d + i] = nb_from_f32<TOut>(0.0f);
-  }
   const int row0 = cu_rows[seq], row1 = cu_rows[seq + 1];
   const int slot = seq_slot[seq];
   if (slot < 0 || row1 <= row0) return;
 
-  const int col = tid / LPC, q = tid % LPC;     // this thread's column and quarter of the keys
+  const int col = col0 + tid / LPC, q = tid % LPC;   // this thread's column and share of the keys
   // the key channel of this thread's i-th state value
   auto channel = [q](int i) { return (((i >> 2) * LPC + q) << 2) + (i & 3); };
   float* st = state + ((size_t)slot * n_heads + h) * d * d;
@@ -78,34 +76,39 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
 
   for (int c0 = row0; c0 < row1; c0 += CHUNK) {
     const int nc = min(CHUNK, row1 - c0);
-    // ---- prepare: a warp per token, lanes over the key channels
+    // ---- prepare: a warp per token, lanes over the key channels, every load issued before the
+    // first is used
     for (int c = warp; c < nc; c += NW) {
-      const float* row = fused + (size_t)(c0 + c) * stride;
+      const float* row = fused + (size_t)(c0 + c) * stride + h * d;
       const float* dl = decay_logits + (size_t)(c0 + c) * hd + h * d;
+      float kx[KIT], rx[KIT], al[KIT], dx[KIT];
       float ss = 0.0f;
-      for (int k = lane; k < d; k += 32) {
-        const float kx = row[col_k + h * d + k];
-        ss = fmaf(kx, kx, ss);
+#pragma unroll
+      for (int j = 0; j < KIT; ++j) {
+        const int k = lane + 32 * j;
+        const bool in = k < d;
+        kx[j] = in ? row[col_k + k] : 0.0f;
+        rx[j] = in ? row[col_r + k] : 0.0f;
+        al[j] = in ? row[col_a + k] : 0.0f;
+        dx[j] = in ? dl[k] : 0.0f;
       }
+      for (int j = lane; j < COLS; j += 32)
+        v_s[c * COLS + j] = (col0 + j < d) ? row[col_v + col0 + j] : 0.0f;
+#pragma unroll
+      for (int j = 0; j < KIT; ++j) ss = fmaf(kx[j], kx[j], ss);
       ss = nb_warp_sum(ss);
       const float inv = 1.0f / sqrtf(ss + key_eps);
-      for (int k = lane; k < DP; k += 32) {
-        float wv = 0.0f, au = 0.0f, u = 0.0f, kx = 0.0f, rx = 0.0f, vx = 0.0f;
-        if (k < d) {
-          kx = row[col_k + h * d + k];
-          rx = row[col_r + h * d + k];
-          vx = row[col_v + h * d + k];
-          u = kx * inv;
-          const float a = nb_sigmoid(row[col_a + h * d + k] + a_bias[h * d + k]);
-          au = a * u;
-          wv = expf(-rate * nb_sigmoid(dl[k]));
-        }
-        w_s[c * DP + k] = wv;
-        au_s[c * DP + k] = au;
+#pragma unroll
+      for (int j = 0; j < KIT; ++j) {
+        const int k = lane + 32 * j;
+        const bool in = k < d;
+        const float u = kx[j] * inv;
+        const float a = in ? nb_sigmoid(al[j] + a_bias[h * d + k]) : 0.0f;
+        w_s[c * DP + k] = in ? expf(-rate * nb_sigmoid(dx[j])) : 0.0f;
+        au_s[c * DP + k] = a * u;
         u_s[c * DP + k] = u;
-        k_s[c * DP + k] = kx;
-        r_s[c * DP + k] = rx;
-        v_s[c * DP + k] = vx;
+        k_s[c * DP + k] = kx[j];
+        r_s[c * DP + k] = rx[j];
       }
     }
     __syncthreads();
@@ -116,7 +119,7 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
       const float4* u4 = reinterpret_cast<const float4*>(u_s + c * DP) + q;
       const float4* k4 = reinterpret_cast<const float4*>(k_s + c * DP) + q;
       const float4* r4 = reinterpret_cast<const float4*>(r_s + c * DP) + q;
-      const float vj = v_s[c * DP + col];
+      const float vj = v_s[c * COLS + tid / LPC];
       float rem = 0.0f;
 #pragma unroll
       for (int g = 0; g < KPL / 4; ++g) {
@@ -126,8 +129,8 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
         rem = fmaf(uu.z, S[4 * g + 2], rem);
         rem = fmaf(uu.w, S[4 * g + 3], rem);
       }
-      rem += __shfl_xor_sync(0xffffffffu, rem, 1);
-      rem += __shfl_xor_sync(0xffffffffu, rem, 2);
+#pragma unroll
+      for (int m = 1; m < LPC; m <<= 1) rem += __shfl_xor_sync(0xffffffffu, rem, m);
       float o = 0.0f;
 #pragma unroll
       for (int g = 0; g < KPL / 4; ++g) {
@@ -141,29 +144,18 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
         o = fmaf(S[4 * g + 2], rr.z, o);
         o = fmaf(S[4 * g + 3], rr.w, o);
       }
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      if (q == 0) o_s[c * DP + col] = o;
+#pragma unroll
+      for (int m = 1; m < LPC; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+      if (q == 0) o_s[c * COLS + tid / LPC] = o;
     }
     __syncthreads();
-    // ---- norm over the head, weight, gate, store: a warp per token
-    for (int c = warp; c < nc; c += NW) {
-      float ss = 0.0f;
-      for (int j = lane; j < d; j += 32) {
-        const float o = o_s[c * DP + j];
-        ss = fmaf(o, o, ss);
-      }
-      ss = nb_warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-      const float* row = fused + (size_t)(c0 + c) * stride;
-      for (int j = lane; j < d; j += 32) {
-        const float g = nb_sigmoid(row[col_g + h * d + j]);
-        out[(size_t)(c0 + c) * hd + h * d + j] =
-            nb_from_f32<TOut>(o_s[c * DP + j] * inv * norm_w[h * d + j] * g);
-      }
+    // ---- the chunk's o, in rows of COLS consecutive floats
+    for (int e = tid; e < nc * COLS; e += THREADS) {
+      const int c = e / COLS, j = e - c * COLS;
+      if (col0 + j < d) o_raw[(size_t)(c0 + c) * hd + h * d + col0 + j] = o_s[e];
     }
-    // the next chunk's preparation writes other arrays than the ones read above, and its
-    // barrier stands between these reads of o_s and the next writes to it
+    // the next chunk's preparation writes other arrays than o_s, and its barrier stands between
+    // these reads of o_s and the next writes to it
   }
 #pragma unroll
   for (int i = 0; i < KPL; ++i) {
@@ -172,19 +164,48 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
   }
 }
 
-template <int DP, typename TOut>
+// out[r, h, :] = o[r, h, :] / sqrt(mean(o[r, h, :]^2) + eps) * norm_w[h, :] * sigmoid(gate logits).
+// A CTA per row, its warps over the heads; padding rows give zeros.
+template <typename TOut>
+__global__ void __launch_bounds__(128)
+delta_finish_kernel(const float* o_raw, const float* fused, int stride, int col_g,
+                    const float* __restrict__ norm_w, float eps, const int* row_slot, TOut* out,
+                    int n_heads, int d) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int hd = n_heads * d;
+  const bool live = row_slot[r] >= 0;
+  for (int h = warp; h < n_heads; h += 4) {
+    TOut* dst = out + (size_t)r * hd + h * d;
+    if (!live) {
+      for (int j = lane; j < d; j += 32) dst[j] = nb_from_f32<TOut>(0.0f);
+      continue;
+    }
+    const float* o = o_raw + (size_t)r * hd + h * d;
+    const float* g = fused + (size_t)r * stride + col_g + h * d;
+    float ss = 0.0f;
+    for (int j = lane; j < d; j += 32) ss = fmaf(o[j], o[j], ss);
+    ss = nb_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int j = lane; j < d; j += 32)
+      dst[j] = nb_from_f32<TOut>(o[j] * inv * norm_w[h * d + j] * nb_sigmoid(g[j]));
+  }
+}
+
+template <int DP, int LPC>
 int launch(cudaStream_t stream, const float* fused, int stride, int col_r, int col_k, int col_v,
-           int col_g, int col_a, const float* decay_logits, const float* a_bias,
-           const float* norm_w, float eps, float rate, float key_eps, const int* cu_rows,
-           const int* seq_slot, float* state, void* out, int n_heads, int d, int n_seqs,
-           int n_rows) {
-  const size_t smem = (size_t)7 * CHUNK * DP * sizeof(float);
-  auto kern = delta_rule_kernel<DP, TOut>;
+           int col_a, const float* decay_logits, const float* a_bias, float rate, float key_eps,
+           const int* cu_rows, const int* seq_slot, float* state, float* o_raw, int n_heads, int d,
+           int n_seqs) {
+  constexpr int COLS = THREADS / LPC;
+  const size_t smem = (size_t)(5 * CHUNK * DP + 2 * CHUNK * COLS) * sizeof(float);
+  auto kern = delta_rule_kernel<DP, LPC>;
   if (smem > 48 * 1024)
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  NB_CUDA(nb_launch(kern, dim3(n_seqs, n_heads), dim3(LPC * DP), smem, stream, fused, stride, col_r,
-                    col_k, col_v, col_g, col_a, decay_logits, a_bias, norm_w, eps, rate, key_eps,
-                    cu_rows, seq_slot, state, (TOut*)out, n_heads, d, n_seqs, n_rows));
+  NB_CUDA(nb_launch(kern, dim3(n_seqs, n_heads, (d + COLS - 1) / COLS), dim3(THREADS), smem, stream,
+                    fused, stride, col_r, col_k, col_v, col_a, decay_logits, a_bias, rate, key_eps,
+                    cu_rows, seq_slot, state, o_raw, n_heads, d));
   return 0;
 }
 
@@ -194,14 +215,15 @@ NB_EXPORT int nb_delta_rule_supported(int d) { return d >= 1 && d <= 256 ? 1 : 0
 
 // fused: fp32 [n_rows][stride] with head h's r, k, v, gate logits and a logits at columns
 // col_x + h*d ..; decay_logits: fp32 [n_rows][n_heads*d]; a_bias, norm_w: fp32 [n_heads*d];
-// state: fp32 [n_slots][n_heads][d][d] (key channel, value channel); out: [n_rows][n_heads*d].
-// cu_rows [n_seqs+1], seq_slot [n_seqs]: the packed batch.
+// state: fp32 [n_slots][n_heads][d][d] (key channel, value channel); o_raw: fp32 scratch
+// [n_rows][n_heads*d]; out: [n_rows][n_heads*d].  cu_rows [n_seqs+1], seq_slot [n_seqs],
+// row_slot [n_rows]: the packed batch.
 NB_EXPORT int nb_delta_rule(const float* fused, int stride, int col_r, int col_k, int col_v,
                             int col_g, int col_a, const float* decay_logits, const float* a_bias,
                             const float* norm_w, float eps, float rate, float key_eps,
-                            const int* cu_rows, const int* seq_slot, float* state, void* out,
-                            int out_dtype, int n_heads, int d, int n_seqs, int n_rows,
-                            cudaStream_t stream) {
+                            const int* cu_rows, const int* seq_slot, const int* row_slot,
+                            float* state, float* o_raw, void* out, int out_dtype, int n_heads,
+                            int d, int n_seqs, int n_rows, cudaStream_t stream) {
   if (n_rows == 0 || n_seqs == 0) return 0;
   NB_REQUIRE(n_heads >= 1 && n_heads <= 65535 && n_seqs > 0 && n_rows > 0, NB_ERR_BAD_ARG,
              "delta_rule: bad sizes heads=%d seqs=%d rows=%d", n_heads, n_seqs, n_rows);
@@ -210,20 +232,24 @@ NB_EXPORT int nb_delta_rule(const float* fused, int stride, int col_r, int col_k
   NB_REQUIRE(out_dtype == NB_F32 || out_dtype == NB_BF16, NB_ERR_BAD_ARG,
              "delta_rule: unknown output dtype %d", out_dtype);
   int rc;
-#define NB_DR(DP)                                                                                 \
-  rc = out_dtype == NB_F32                                                                        \
-           ? launch<DP, float>(stream, fused, stride, col_r, col_k, col_v, col_g, col_a,          \
-                               decay_logits, a_bias, norm_w, eps, rate, key_eps, cu_rows,         \
-                               seq_slot, state, out, n_heads, d, n_seqs, n_rows)                  \
-           : launch<DP, __nv_bfloat16>(stream, fused, stride, col_r, col_k, col_v, col_g, col_a,  \
-                                       decay_logits, a_bias, norm_w, eps, rate, key_eps, cu_rows, \
-                                       seq_slot, state, out, n_heads, d, n_seqs, n_rows)
-  if (d <= 32) NB_DR(32);
-  else if (d <= 64) NB_DR(64);
-  else if (d <= 128) NB_DR(128);
-  else NB_DR(256);
+#define NB_DR(DP, LPC)                                                                            \
+  rc = launch<DP, LPC>(stream, fused, stride, col_r, col_k, col_v, col_a, decay_logits, a_bias,   \
+                       rate, key_eps, cu_rows, seq_slot, state, o_raw, n_heads, d, n_seqs)
+  // lanes per column: as many as leave a lane at least eight channels (four for small heads),
+  // so that a head of 64 and more is spread over several CTAs
+  if (d <= 32) NB_DR(32, 8);
+  else if (d <= 64) NB_DR(64, 8);
+  else if (d <= 128) NB_DR(128, 8);
+  else NB_DR(256, 8);
 #undef NB_DR
   if (rc != 0) return rc;
   NB_CHECK_LAUNCH("delta_rule");
+  if (out_dtype == NB_F32)
+    NB_CUDA(nb_launch(delta_finish_kernel<float>, dim3(n_rows), dim3(128), 0, stream, o_raw, fused,
+                      stride, col_g, norm_w, eps, row_slot, (float*)out, n_heads, d));
+  else
+    NB_CUDA(nb_launch(delta_finish_kernel<__nv_bfloat16>, dim3(n_rows), dim3(128), 0, stream, o_raw,
+                      fused, stride, col_g, norm_w, eps, row_slot, (__nv_bfloat16*)out, n_heads, d));
+  NB_CHECK_LAUNCH("delta_finish");
   return 0;
 }

@@ -704,10 +704,15 @@ class CudaBackend:
                 norm_w.numel() != hd or state.shape[1] != hd * dim or \
                 fused.shape[1] < max(col_r, col_k, col_v, col_g, col_a) + hd:
             raise KernelError("delta_rule: shapes do not agree")
+        # the heads' outputs before their norm (the recurrence runs a head's columns in several
+        # CTAs; the norm over the head is a pass of its own)
+        o_raw = torch.empty((n, hd), device=out.device, dtype=torch.float32)
         self._call("nb_delta_rule", _ptr(fused), fused.shape[1], col_r, col_k, col_v, col_g, col_a,
                    _ptr(decay_logits), _ptr(a_bias), _ptr(norm_w), float(eps), float(decay_rate),
-                   float(key_eps), _ptr(layout.cu_rows), _ptr(layout.seq_slot), _ptr(state), _ptr(out),
-                   dtype_code(out.dtype), n_heads, dim, layout.n_seqs, n, self._stream())
+                   float(key_eps), _ptr(layout.cu_rows), _ptr(layout.seq_slot), _ptr(layout.row_slot),
+                   _ptr(state), _ptr(o_raw), _ptr(out), dtype_code(out.dtype), n_heads, dim,
+                   layout.n_seqs, n, self._stream())
+        self.launches += 1
 
     # -- routed experts ---------------------------------------------------------------
     def moe_route(self, logits, col, n_experts, top, renormalize, layout, idx, weight):

@@ -58,7 +58,7 @@ SIGNATURES = {
     "nb_attention_pooled_mma": "piippppppipppiiiiippiifiiiip",
     "nb_attention_pooled": "pipppppipppiiiiiippifiiip",
     "nb_delta_rule_supported": "i",
-    "nb_delta_rule": "piiiiiipppfffppppiiiiip",
+    "nb_delta_rule": "piiiiiipppfffppppppiiiiip",
     "nb_layernorm": "pppppiiifp",
     "nb_rmsnorm": "piipppiiifp",
     "nb_latent_append": "piipfpppipiiiip",
