@@ -74,43 +74,69 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
     S[i] = (k < d && col < d) ? st[(size_t)k * d + col] : 0.0f;
   }
 
-  for (int c0 = row0; c0 < row1; c0 += CHUNK) {
-    const int nc = min(CHUNK, row1 - c0);
-    // ---- prepare: a warp per token, lanes over the key channels, every load issued before the
-    // first is used
-    for (int c = warp; c < nc; c += NW) {
-      const float* row = fused + (size_t)(c0 + c) * stride + h * d;
-      const float* dl = decay_logits + (size_t)(c0 + c) * hd + h * d;
-      float kx[KIT], rx[KIT], al[KIT], dx[KIT];
-      float ss = 0.0f;
+  // A warp prepares the tokens warp and warp + NW of a chunk.  Their rows are fetched into
+  // registers a chunk ahead (PREFETCH), so that the trip to memory runs under the recurrence.
+  constexpr int TPW = CHUNK / NW;
+  constexpr bool PREFETCH = DP <= 128;
+  float kx[TPW][KIT], rx[TPW][KIT], al[TPW][KIT], dx[TPW][KIT], vx[TPW][(COLS + 31) / 32];
+  auto fetch = [&](int c0) {
+#pragma unroll
+    for (int t = 0; t < TPW; ++t) {
+      const int r = c0 + warp + t * NW;
+      const bool live = r < row1;
+      const float* row = fused + (size_t)(live ? r : row0) * stride + h * d;
+      const float* dl = decay_logits + (size_t)(live ? r : row0) * hd + h * d;
 #pragma unroll
       for (int j = 0; j < KIT; ++j) {
         const int k = lane + 32 * j;
-        const bool in = k < d;
-        kx[j] = in ? row[col_k + k] : 0.0f;
-        rx[j] = in ? row[col_r + k] : 0.0f;
-        al[j] = in ? row[col_a + k] : 0.0f;
-        dx[j] = in ? dl[k] : 0.0f;
+        const bool in = live && k < d;
+        kx[t][j] = in ? row[col_k + k] : 0.0f;
+        rx[t][j] = in ? row[col_r + k] : 0.0f;
+        al[t][j] = in ? row[col_a + k] : 0.0f;
+        dx[t][j] = in ? dl[k] : 0.0f;
       }
-      for (int j = lane; j < COLS; j += 32)
-        v_s[c * COLS + j] = (col0 + j < d) ? row[col_v + col0 + j] : 0.0f;
 #pragma unroll
-      for (int j = 0; j < KIT; ++j) ss = fmaf(kx[j], kx[j], ss);
+      for (int j = 0; j < (COLS + 31) / 32; ++j) {
+        const int c = lane + 32 * j;
+        vx[t][j] = (live && c < COLS && col0 + c < d) ? row[col_v + col0 + c] : 0.0f;
+      }
+    }
+  };
+  if (PREFETCH) fetch(row0);
+
+  for (int c0 = row0; c0 < row1; c0 += CHUNK) {
+    const int nc = min(CHUNK, row1 - c0);
+    // ---- prepare: a warp per token, lanes over the key channels
+    if (!PREFETCH) fetch(c0);
+#pragma unroll
+    for (int t = 0; t < TPW; ++t) {
+      const int c = warp + t * NW;
+      if (c >= nc) continue;
+      float ss = 0.0f;
+#pragma unroll
+      for (int j = 0; j < KIT; ++j) ss = fmaf(kx[t][j], kx[t][j], ss);
       ss = nb_warp_sum(ss);
       const float inv = 1.0f / sqrtf(ss + key_eps);
 #pragma unroll
       for (int j = 0; j < KIT; ++j) {
         const int k = lane + 32 * j;
         const bool in = k < d;
-        const float u = kx[j] * inv;
-        const float a = in ? nb_sigmoid(al[j] + a_bias[h * d + k]) : 0.0f;
-        w_s[c * DP + k] = in ? expf(-rate * nb_sigmoid(dx[j])) : 0.0f;
+        const float u = kx[t][j] * inv;
+        const float a = in ? nb_sigmoid(al[t][j] + a_bias[h * d + k]) : 0.0f;
+        w_s[c * DP + k] = in ? expf(-rate * nb_sigmoid(dx[t][j])) : 0.0f;
         au_s[c * DP + k] = a * u;
         u_s[c * DP + k] = u;
-        k_s[c * DP + k] = kx[j];
-        r_s[c * DP + k] = rx[j];
+        k_s[c * DP + k] = kx[t][j];
+        r_s[c * DP + k] = rx[t][j];
+      }
+#pragma unroll
+      for (int j = 0; j < (COLS + 31) / 32; ++j) {
+        const int cc = lane + 32 * j;
+        if (cc < COLS) v_s[c * COLS + cc] = vx[t][j];
       }
     }
+    __syncthreads();
+    if (PREFETCH && c0 + CHUNK < row1) fetch(c0 + CHUNK);
     __syncthreads();
     // ---- the recurrence: every thread walks the chunk's tokens in order
     for (int c = 0; c < nc; ++c) {
@@ -120,18 +146,19 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
       const float4* k4 = reinterpret_cast<const float4*>(k_s + c * DP) + q;
       const float4* r4 = reinterpret_cast<const float4*>(r_s + c * DP) + q;
       const float vj = v_s[c * COLS + tid / LPC];
-      float rem = 0.0f;
+      float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;     // four chains, added up at the end
 #pragma unroll
       for (int g = 0; g < KPL / 4; ++g) {
         const float4 uu = u4[g * LPC];
-        rem = fmaf(uu.x, S[4 * g], rem);
-        rem = fmaf(uu.y, S[4 * g + 1], rem);
-        rem = fmaf(uu.z, S[4 * g + 2], rem);
-        rem = fmaf(uu.w, S[4 * g + 3], rem);
+        r0 = fmaf(uu.x, S[4 * g], r0);
+        r1 = fmaf(uu.y, S[4 * g + 1], r1);
+        r2 = fmaf(uu.z, S[4 * g + 2], r2);
+        r3 = fmaf(uu.w, S[4 * g + 3], r3);
       }
+      float rem = (r0 + r1) + (r2 + r3);
 #pragma unroll
       for (int m = 1; m < LPC; m <<= 1) rem += __shfl_xor_sync(0xffffffffu, rem, m);
-      float o = 0.0f;
+      float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
       for (int g = 0; g < KPL / 4; ++g) {
         const float4 ww = w4[g * LPC], aa = au4[g * LPC], kk = k4[g * LPC], rr = r4[g * LPC];
@@ -139,11 +166,12 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
         S[4 * g + 1] = fmaf(kk.y, vj, fmaf(ww.y, S[4 * g + 1], -aa.y * rem));
         S[4 * g + 2] = fmaf(kk.z, vj, fmaf(ww.z, S[4 * g + 2], -aa.z * rem));
         S[4 * g + 3] = fmaf(kk.w, vj, fmaf(ww.w, S[4 * g + 3], -aa.w * rem));
-        o = fmaf(S[4 * g], rr.x, o);
-        o = fmaf(S[4 * g + 1], rr.y, o);
-        o = fmaf(S[4 * g + 2], rr.z, o);
-        o = fmaf(S[4 * g + 3], rr.w, o);
+        o0 = fmaf(S[4 * g], rr.x, o0);
+        o1 = fmaf(S[4 * g + 1], rr.y, o1);
+        o2 = fmaf(S[4 * g + 2], rr.z, o2);
+        o3 = fmaf(S[4 * g + 3], rr.w, o3);
       }
+      float o = (o0 + o1) + (o2 + o3);
 #pragma unroll
       for (int m = 1; m < LPC; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
       if (q == 0) o_s[c * COLS + tid / LPC] = o;
