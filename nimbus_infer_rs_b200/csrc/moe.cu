@@ -264,7 +264,7 @@ NB_EXPORT int nb_moe_gemm_tiles(int n_pairs, int n_experts) {
 
 // y[place, :] = f(x[row(place), :]) for every place of every expert's group, where
 // row(place) = order[place] / row_div if `order` is given, else place itself;
-// f = x We^T, or act(x We^T) * (x We2^T) when W2 is given.  W, W2: [n_experts][N][K].
+// f = act(x We^T), or act(x We^T) * (x We2^T) when W2 is given.  W, W2: [n_experts][N][K].
 NB_EXPORT int nb_moe_gemm(const void* x, int x_dtype, int x_stride, const int* order, int row_div,
                           const int* offsets, int n_experts, int n_pairs, const void* W,
                           const void* W2, int w_dtype, void* y, int y_dtype, int y_stride, int N,
