@@ -19,7 +19,8 @@
 // Tokens are taken CHUNK at a time: all threads prepare the chunk's vectors (w, a*u, u, k, r and
 // the CTA's part of v) in shared memory, a warp per token with one trip to memory; then every
 // thread walks the chunk's tokens in order without a barrier; then the chunk's o goes out in
-// fp32.  A second kernel norms each head's o, applies weight and gate and writes the output type
+// fp32, each lane's part of it added up there (not with shuffles inside the chain from one
+// token's state to the next).  A second kernel norms each head's o, applies weight and gate and writes the output type
 // (the norm needs all of a head's columns).  The state is read from the sequence's state row
 // before the first token of the step and written back after the last, so a sequence may be cut
 // into steps anywhere: the arithmetic per token does not depend on the cut, nor on what else is
@@ -54,7 +55,7 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
   float* k_s = u_s + CHUNK * DP;
   float* r_s = k_s + CHUNK * DP;
   float* v_s = r_s + CHUNK * DP;                // [CHUNK][COLS]
-  float* o_s = v_s + CHUNK * COLS;              // [CHUNK][COLS]
+  float* o_s = v_s + CHUNK * COLS;              // [CHUNK][COLS][LPC]: every lane's part of o
 
   const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS, tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -137,8 +138,8 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
     }
     __syncthreads();
     if (PREFETCH && c0 + CHUNK < row1) fetch(c0 + CHUNK);
-    __syncthreads();
     // ---- the recurrence: every thread walks the chunk's tokens in order
+#pragma unroll 2
     for (int c = 0; c < nc; ++c) {
       const float4* w4 = reinterpret_cast<const float4*>(w_s + c * DP) + q;
       const float4* au4 = reinterpret_cast<const float4*>(au_s + c * DP) + q;
@@ -171,16 +172,19 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
         o2 = fmaf(S[4 * g + 2], rr.z, o2);
         o3 = fmaf(S[4 * g + 3], rr.w, o3);
       }
-      float o = (o0 + o1) + (o2 + o3);
-#pragma unroll
-      for (int m = 1; m < LPC; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-      if (q == 0) o_s[c * COLS + tid / LPC] = o;
+      // this lane's part of o; the lanes' parts are added up when the chunk goes out, off the
+      // chain from one token's state to the next
+      o_s[c * THREADS + tid] = (o0 + o1) + (o2 + o3);
     }
     __syncthreads();
     // ---- the chunk's o, in rows of COLS consecutive floats
     for (int e = tid; e < nc * COLS; e += THREADS) {
       const int c = e / COLS, j = e - c * COLS;
-      if (col0 + j < d) o_raw[(size_t)(c0 + c) * hd + h * d + col0 + j] = o_s[e];
+      const float* part = o_s + c * THREADS + j * LPC;
+      float o = 0.0f;
+#pragma unroll
+      for (int m = 0; m < LPC; ++m) o += part[m];
+      if (col0 + j < d) o_raw[(size_t)(c0 + c) * hd + h * d + col0 + j] = o;
     }
     // the next chunk's preparation writes other arrays than o_s, and its barrier stands between
     // these reads of o_s and the next writes to it
@@ -227,7 +231,7 @@ int launch(cudaStream_t stream, const float* fused, int stride, int col_r, int c
            const int* cu_rows, const int* seq_slot, float* state, float* o_raw, int n_heads, int d,
            int n_seqs) {
   constexpr int COLS = THREADS / LPC;
-  const size_t smem = (size_t)(5 * CHUNK * DP + 2 * CHUNK * COLS) * sizeof(float);
+  const size_t smem = (size_t)(5 * CHUNK * DP + CHUNK * COLS + CHUNK * THREADS) * sizeof(float);
   auto kern = delta_rule_kernel<DP, LPC>;
   if (smem > 48 * 1024)
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -263,10 +267,12 @@ NB_EXPORT int nb_delta_rule(const float* fused, int stride, int col_r, int col_k
 #define NB_DR(DP, LPC)                                                                            \
   rc = launch<DP, LPC>(stream, fused, stride, col_r, col_k, col_v, col_a, decay_logits, a_bias,   \
                        rate, key_eps, cu_rows, seq_slot, state, o_raw, n_heads, d, n_seqs)
-  // lanes per column: as many as leave a lane at least eight channels (four for small heads),
-  // so that a head of 64 and more is spread over several CTAs
+  // Lanes per column, as measured on prompts of 1,024 tokens: 16 (four channels a lane) up to
+  // 64 channels, 8 above (two and four lanes a column, and four columns a thread with the
+  // token's vectors shared among them, were slower: fewer warps in flight).  A CTA takes 16 or
+  // 32 of a head's columns, so a head is spread over 2 to 8 CTAs.
   if (d <= 32) NB_DR(32, 8);
-  else if (d <= 64) NB_DR(64, 8);
+  else if (d <= 64) NB_DR(64, 16);
   else if (d <= 128) NB_DR(128, 8);
   else NB_DR(256, 8);
 #undef NB_DR
