@@ -219,7 +219,7 @@ class RizitarConfig:
         total += self.vocab_size * self.side_dim * len(self.layers)
         for l in self.layers:
             m = l.mixer
-            total += 4 * D + (2 * self.side_dim * D + D if self.side_dim else 0)
+            total += (4 if l.mlp is not None else 2) * D + (2 * self.side_dim * D + D if self.side_dim else 0)
             if l.type == "general_delta":
                 hd, r = m.heads * m.dim, m.decay_rank or 0
                 total += 6 * hd * D + r * D + hd * r + 3 * hd

@@ -224,3 +224,48 @@ def test_random_weights_mode_and_inspect(cpu_backend):
     assert out.shape == (1, 257) and torch.isfinite(out).all()
     info = e.inspect()
     assert info["architecture"] == "rizitar" and info["layers"] == 4 and info["tie_head"] is True
+
+
+def test_command_line_and_trace_replay_take_the_design(cpu_backend, tmp_path, monkeypatch, capsys):
+    """`random` writes a Rizitar folder from a preset (its config.json carries the decay's rank,
+    so the folder reads back without the hook on the shapes too); `trace_run` replays steps on it."""
+    import importlib.machinery
+    import importlib.util
+    import io
+    import json
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    from nimbus_infer_rs_b200.__main__ import main
+    from nimbus_infer_rs_b200.weights.safetensors_io import SafeTensorsFile
+    folder = tmp_path / "m"
+    assert main(["random", "--out", str(folder), "--preset", "rizitar-tiny", "--seed", "3"]) == 0
+    wrote = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    cfg = json.loads((folder / "config.json").read_text())
+    assert cfg["architecture"] == "Rizitar" and cfg["layers"][0]["mixer"]["decay_rank"] == 8
+    with SafeTensorsFile(folder / "model.safetensors") as f:
+        assert wrote["n_params"] == sum(f.tensor(n).numel() for n in f.names())
+        P = {n: f.tensor(n).float() for n in f.names()}
+    Engine.load(folder, dtype="float32", device="cpu", cache_tokens=128)
+
+    root = Path(__file__).resolve().parent.parent
+    loader = importlib.machinery.SourceFileLoader("trace_run_program", str(root / "bin" / "trace_run"))
+    mod = importlib.util.module_from_spec(importlib.util.spec_from_loader(loader.name, loader))
+    loader.exec_module(mod)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3, 4], "want": [1, 3]},
+                                     {"id": "b", "tokens": [9], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": [5], "want": [0]},
+                                     {"id": "b", "tokens": [8], "want": [0]}], "end": ["a", "b"]}]
+    out = tmp_path / "out"
+    monkeypatch.setattr(sys, "argv", ["trace_run", "--model", str(folder), "--dtype", "float32", "--out",
+                                      str(out), "--max-tokens", "128", "--device", "cpu"])
+    monkeypatch.setattr(sys, "stdin", io.StringIO("".join(json.dumps(s) + "\n" for s in steps)))
+    assert mod.main() == 0
+    assert [l for l in capsys.readouterr().out.split("\n") if l] == ["done 0", "done 1"]
+    a, b = PZ.forward(cfg, P, [1, 2, 3, 4, 5]), PZ.forward(cfg, P, [9, 8])
+    got0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1))
+    got1 = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(2, -1))
+    _close(got0, a[[1, 3]])
+    _close(got1, torch.stack([a[4], b[1]]))
