@@ -72,7 +72,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
   const int q0 = tile * BLOCK_Q;
   if (q0 >= n_q) return;
   const int slot = seq_slot[s];
-  if (slot < 0) return;
+  if (slot < 0) {
+    // a sequence that has ended (a decode session keeps its row): zeros, not what the buffer held
+    if (EXTRA)
+      for (int i = threadIdx.x; i < min(BLOCK_Q, n_q - q0) * HD; i += THREADS)
+        out[(size_t)(row0 + q0 + i / HD) * out_stride + h * HD + i % HD] = nb_from_f32<TOut>(0.0f);
+    return;
+  }
   const int pos0 = seq_pos0[s];
   const int kvh = h / group;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

@@ -258,6 +258,22 @@ def test_bfloat16_generation_runs_in_a_recorded_decode_session(models):
     assert a == b and all(len(x) == 20 for x in a)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_row_that_stops_early_leaves_the_others_alone(models, dtype):
+    """A sequence that meets a stop token becomes a padding row of the decode session; the others
+    go on exactly as they do without the stop."""
+    e = _engine(models, "B", dtype, cache_tokens=8 * 64)
+    prompts = [_tokens(320, n, 7 + n) for n in (12, 70, 3)]
+    free = e.generate(prompts, SamplingParams(max_new_tokens=16, temperature=0.0))
+    stop = free[0][4]
+    out = e.generate(prompts, SamplingParams(max_new_tokens=16, temperature=0.0, stop_tokens=[stop]))
+    assert len(out[0]) <= 5
+    for f, o in zip(free, out):
+        cut = f.index(stop) + 1 if stop in f else len(f)
+        assert o == f[:cut]
+    assert e.cache.slots.n_free == e.cache.n_slots
+
+
 def test_the_comparison_sees_a_left_out_mechanism(models):
     """The tests above would not notice a mechanism that changes nothing: change each in the
     plain implementation and see the engine's logits move away by far more than the tolerance."""
