@@ -77,8 +77,15 @@ CONFIGS = {
         delta(2, 96, mlp=dense(16)),
     ]},
 }
-SEEDS = {"A": 11, "B": 12, "C": 13, "D": 14}
-DECAY_RANK = {"A": 6, "B": 8, "C": 1, "D": 5}
+# E: nothing is a multiple of 8 (the products' and the attention's paths for ragged sizes)
+CONFIGS["E"] = {"architecture": "Rizitar", "vocab": 333, "width": 100, "norm": {"eps": 2e-6},
+                "embedding": {"scale": 10.0}, "token_side": {"dim": 7}, "layers": [
+    delta(3, 10, mlp=moe(5, 2, 30)),
+    attn(5, 5, 20, 0.22, size=50, pool=3, rot=rot(10, 777.0, (3.0, 100, 5.0, 1.0)), mlp=dense(50)),
+    attn(6, 2, 12, 0.3, size=13, pool=11, rot=rot(12, 2000.0), mlp=None),
+]}
+SEEDS = {"A": 11, "B": 12, "C": 13, "D": 14, "E": 15}
+DECAY_RANK = {"A": 6, "B": 8, "C": 1, "D": 5, "E": 3}
 
 
 def make_tensors(cfg: dict, seed: int, decay_rank: int, sink_std: float = 1.5) -> dict[str, torch.Tensor]:

@@ -13,7 +13,7 @@ from gpu_helpers import DTYPES
 from nimbus_infer_rs_b200 import Engine, SamplingParams
 
 pytestmark = pytest.mark.gpu
-NAMES = ["A", "B", "C", "D"]
+NAMES = ["A", "B", "C", "D", "E"]
 # A router's choice between experts whose logits are closer than this may be settled either way
 # by rounding; the plain implementation then follows the engine.
 MARGIN = {"float32": 1e-3, "bfloat16": 1.0}

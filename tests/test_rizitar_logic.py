@@ -99,7 +99,7 @@ def test_rotary_frequencies_against_the_plain_ones():
         assert torch.allclose(f.double(), pf, rtol=1e-7, atol=0) and abs(amp - pamp) < 1e-12
 
 
-@pytest.mark.parametrize("name", ["A", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "C", "D", "E"])
 def test_whole_prompts_and_token_by_token(models, cpu_backend, name):
     _, cfg, P = models[name]
     e = _engine(models, name)
