@@ -9,8 +9,7 @@ from .attention import CausalSelfAttention
 from .latent_attention import LatentAttention
 from .feed_forward import DenseMLP
 from .routed_experts import RoutedExperts
-from .block import ParallelBlock, PreNormBlock
+from .block import ParallelBlock, PreNormBlock, SandwichBlock
 from .pooled_attention import PooledWindowAttention
 from .delta_rule import DeltaRule
 from .token_side import GatedTokenInput
-from .block import SandwichBlock
