@@ -390,6 +390,95 @@ __global__ void rms_add_kernel(const float* y, const float* __restrict__ gamma, 
   }
 }
 
+// The same with a warp per row and the row in registers, 16 bytes a load (width a multiple of
+// 128, at most RW_MAX * 128): no barrier, the two sums by shuffles.
+constexpr int RW_MAX = 16;
+
+template <typename TOut>
+__device__ __forceinline__ void nb_store4(TOut* p, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void nb_store4<float>(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void nb_store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c,
+                                                        float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&lo);
+  u.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TOut, int NV>
+__global__ void __launch_bounds__(128)
+rms_add_warp_kernel(const float* y, const float* __restrict__ gamma, float eps, float* x,
+                    const float* __restrict__ next_gamma, float next_eps, TOut* out_next,
+                    TOut* out_cast, int d, int n_rows) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const float4* yr = reinterpret_cast<const float4*>(y + (size_t)r * d);
+  float4* xr = reinterpret_cast<float4*>(x + (size_t)r * d);
+  const float4* g4 = reinterpret_cast<const float4*>(gamma);
+  float4 v[NV], xv[NV];
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    v[j] = yr[j * 32 + lane];
+    xv[j] = xr[j * 32 + lane];
+  }
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+    ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
+  ss = nb_warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+  float s2 = 0.0f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const float4 g = g4[j * 32 + lane];
+    v[j].x = xv[j].x + v[j].x * inv * g.x;
+    v[j].y = xv[j].y + v[j].y * inv * g.y;
+    v[j].z = xv[j].z + v[j].z * inv * g.z;
+    v[j].w = xv[j].w + v[j].w * inv * g.w;
+    xr[j * 32 + lane] = v[j];
+    if (out_cast != nullptr)
+      nb_store4<TOut>(out_cast + (size_t)r * d + (j * 32 + lane) * 4, v[j].x, v[j].y, v[j].z, v[j].w);
+    s2 = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, s2))));
+  }
+  if (out_next == nullptr) return;
+  s2 = nb_warp_sum(s2);
+  const float inv2 = 1.0f / sqrtf(s2 / (float)d + next_eps);
+  const float4* n4 = reinterpret_cast<const float4*>(next_gamma);
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const float4 g = n4[j * 32 + lane];
+    nb_store4<TOut>(out_next + (size_t)r * d + (j * 32 + lane) * 4, v[j].x * inv2 * g.x,
+                    v[j].y * inv2 * g.y, v[j].z * inv2 * g.z, v[j].w * inv2 * g.w);
+  }
+}
+
+template <typename TOut>
+static int rms_add_warp(int nv, cudaStream_t stream, const float* y, const float* gamma, float eps,
+                        float* x, const float* next_gamma, float next_eps, void* out_next,
+                        void* out_cast, int d, int n_rows) {
+  const dim3 grid((n_rows + 3) / 4), block(128);
+#define NB_RW(NV_)                                                                              \
+  case NV_:                                                                                     \
+    NB_CUDA(nb_launch(rms_add_warp_kernel<TOut, NV_>, grid, block, 0, stream, y, gamma, eps, x, \
+                      next_gamma, next_eps, (TOut*)out_next, (TOut*)out_cast, d, n_rows));      \
+    break;
+  switch (nv) {
+    NB_RW(1) NB_RW(2) NB_RW(3) NB_RW(4) NB_RW(5) NB_RW(6) NB_RW(7) NB_RW(8) NB_RW(9) NB_RW(10)
+    NB_RW(11) NB_RW(12) NB_RW(13) NB_RW(14) NB_RW(15) NB_RW(16)
+    default: return NB_ERR_UNSUPPORTED;
+  }
+#undef NB_RW
+  return 0;
+}
+
 NB_EXPORT int nb_rms_add(const float* y, const float* gamma, float eps, float* x,
                          const float* next_gamma, float next_eps, void* out_next, void* out_cast,
                          int out_dtype, int n_rows, int d, cudaStream_t stream) {
@@ -398,6 +487,21 @@ NB_EXPORT int nb_rms_add(const float* y, const float* gamma, float eps, float* x
              "rms_add: bad sizes rows=%d d=%d", n_rows, d);
   NB_REQUIRE(gamma != nullptr && (out_next == nullptr || next_gamma != nullptr), NB_ERR_BAD_ARG,
              "rms_add: a norm without its weight");
+  NB_REQUIRE(out_dtype == NB_F32 || out_dtype == NB_BF16, NB_ERR_BAD_ARG,
+             "rms_add: unknown output dtype %d", out_dtype);
+  // many rows of a width that a warp holds in registers: a warp per row
+  const bool aligned = (((uintptr_t)y | (uintptr_t)x | (uintptr_t)gamma | (uintptr_t)next_gamma |
+                         (uintptr_t)out_next | (uintptr_t)out_cast) & 15) == 0;
+  if (d % 128 == 0 && d <= RW_MAX * 128 && n_rows >= 64 && aligned) {
+    const int rc = out_dtype == NB_F32
+                       ? rms_add_warp<float>(d / 128, stream, y, gamma, eps, x, next_gamma, next_eps,
+                                             out_next, out_cast, d, n_rows)
+                       : rms_add_warp<__nv_bfloat16>(d / 128, stream, y, gamma, eps, x, next_gamma,
+                                                     next_eps, out_next, out_cast, d, n_rows);
+    if (rc != 0) return rc;
+    NB_CHECK_LAUNCH("rms_add");
+    return 0;
+  }
   int threads = 64;
   while (threads < 1024 && threads * (d > 2048 ? RA_MAX : 4) < d) threads *= 2;
   if (out_dtype == NB_F32)

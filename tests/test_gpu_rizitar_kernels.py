@@ -60,6 +60,26 @@ def test_norm_of_a_result_added_to_the_stream(ops, dtype, d):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d", [128, 384, 2048])
+def test_norm_of_a_result_added_to_the_stream_a_warp_per_row(ops, dtype, d):
+    """Many rows of a width that is a multiple of 128: the variant with a warp per row."""
+    n = 70
+    y, x = _rnd(n, d, seed=1, s=3.0), _rnd(n, d, seed=2)
+    g, g2 = _rnd(d, seed=3) + 1.0, _rnd(d, seed=4) + 1.0
+    x1 = x.double() + PZ.rms_norm(y.double(), g.double(), 1e-5)
+    for with_next, with_cast in ((True, False), (False, True), (False, False), (True, True)):
+        xd = x.to(DEV)
+        nxt = torch.empty(n, d, device=DEV, dtype=ACT[dtype]) if with_next else None
+        cast = torch.empty(n, d, device=DEV, dtype=ACT[dtype]) if with_cast else None
+        ops.rms_add(y.to(DEV), g.to(DEV), 1e-5, xd, g2.to(DEV) if with_next else None, 3e-4, nxt, cast)
+        _close(xd, x1, 2e-6, "stream")
+        if with_next:
+            _close(nxt, PZ.rms_norm(x1, g2.double(), 3e-4), TOL[dtype] / 2, "next norm")
+        if with_cast:
+            _close(cast, x1, TOL[dtype] / 2, "rounded stream")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_row_activations_and_the_gathered_gate(ops, dtype):
     n, d, col = 13, 37, 5
     x = _rnd(n, col + d + 3, seed=5, s=3.0)
