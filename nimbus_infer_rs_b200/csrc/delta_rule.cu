@@ -43,7 +43,6 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
                   float key_eps, const int* cu_rows, const int* seq_slot, float* state,
                   float* o_raw, int n_heads, int d) {
   nb_grid_dependency_wait();
-  nb_launch_dependents();
   constexpr int KPL = DP / LPC;                 // key channels per lane
   constexpr int COLS = THREADS / LPC;           // columns of the state per CTA
   constexpr int KIT = DP / 32;                  // key channels per lane of a preparing warp
@@ -189,6 +188,7 @@ delta_rule_kernel(const float* fused, int stride, int col_r, int col_k, int col_
     // the next chunk's preparation writes other arrays than o_s, and its barrier stands between
     // these reads of o_s and the next writes to it
   }
+  nb_launch_dependents();
 #pragma unroll
   for (int i = 0; i < KPL; ++i) {
     const int k = channel(i);
@@ -229,15 +229,22 @@ template <int DP, int LPC>
 int launch(cudaStream_t stream, const float* fused, int stride, int col_r, int col_k, int col_v,
            int col_a, const float* decay_logits, const float* a_bias, float rate, float key_eps,
            const int* cu_rows, const int* seq_slot, float* state, float* o_raw, int n_heads, int d,
-           int n_seqs) {
+           int n_seqs, bool long_walk) {
   constexpr int COLS = THREADS / LPC;
   const size_t smem = (size_t)(5 * CHUNK * DP + CHUNK * COLS + CHUNK * THREADS) * sizeof(float);
   auto kern = delta_rule_kernel<DP, LPC>;
   if (smem > 48 * 1024)
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  NB_CUDA(nb_launch(kern, dim3(n_seqs, n_heads, (d + COLS - 1) / COLS), dim3(THREADS), smem, stream,
-                    fused, stride, col_r, col_k, col_v, col_a, decay_logits, a_bias, rate, key_eps,
-                    cu_rows, seq_slot, state, o_raw, n_heads, d));
+  const dim3 grid(n_seqs, n_heads, (d + COLS - 1) / COLS);
+  // a prompt's walk runs long on few CTAs: it never overlaps its predecessor (nb_launch_serial)
+  if (long_walk)
+    NB_CUDA(nb_launch_serial(kern, grid, dim3(THREADS), smem, stream, fused, stride, col_r, col_k,
+                             col_v, col_a, decay_logits, a_bias, rate, key_eps, cu_rows, seq_slot,
+                             state, o_raw, n_heads, d));
+  else
+    NB_CUDA(nb_launch(kern, grid, dim3(THREADS), smem, stream, fused, stride, col_r, col_k, col_v,
+                      col_a, decay_logits, a_bias, rate, key_eps, cu_rows, seq_slot, state, o_raw,
+                      n_heads, d));
   return 0;
 }
 
@@ -266,7 +273,8 @@ NB_EXPORT int nb_delta_rule(const float* fused, int stride, int col_r, int col_k
   int rc;
 #define NB_DR(DP, LPC)                                                                            \
   rc = launch<DP, LPC>(stream, fused, stride, col_r, col_k, col_v, col_a, decay_logits, a_bias,   \
-                       rate, key_eps, cu_rows, seq_slot, state, o_raw, n_heads, d, n_seqs)
+                       rate, key_eps, cu_rows, seq_slot, state, o_raw, n_heads, d, n_seqs,        \
+                       n_rows > 4 * n_seqs)
   // Lanes per column, as measured on prompts of 1,024 tokens: 16 (four channels a lane) up to
   // 64 channels, 8 above (two and four lanes a column, and four columns a thread with the
   // token's vectors shared among them, were slower: fewer warps in flight).  A CTA takes 16 or
