@@ -61,7 +61,7 @@ CONFIGS = {
           "embedding": {"scale": 1.0}, "layers": [
         delta(2, 64, mlp=moe(4, 4, 64)),
         attn(8, 2, 32, 0.18, size=128, pool=16, rot=rot(32, 10000.0, (2.0, 256, 16.0, 2.0)), mlp=dense(256)),
-        attn(4, 1, 64, 0.125, size=130, pool=32, rot=rot(16, 10000.0), mlp=moe(8, 3, 32)),
+        attn(4, 1, 64, 0.12, size=130, pool=32, rot=rot(16, 10000.0), mlp=moe(8, 3, 32)),
     ]},
     "C": {"architecture": "Rizitar", "vocab": 31, "width": 8, "norm": {"eps": 1e-5},
           "embedding": {"scale": 0.5}, "token_side": {"dim": 1}, "layers": [
